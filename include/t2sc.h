@@ -1,0 +1,127 @@
+/*
+ * t2sc — B200 (sm_100a) sparse-convolution operators behind a plain C ABI.
+ *
+ * Drop-in boundary for the sparse-convolution path of suvadityamuk/trellis2-cuda.  Every entry point
+ * names the reference interface it replaces (paths are relative to that project).  All pointers are
+ * DEVICE pointers owned by the caller unless a parameter is suffixed `_host`; all work is enqueued on
+ * the context's stream; every function returns a status (0 = ok, negative = error) and never throws.
+ * After a non-zero return, t2sc_last_error() gives the message (the reference's REQ / CK messages,
+ * src/core.h:15-17, surfaced the way apps/t2lib.cu:14-23 surfaces them: code + last-error string).
+ *
+ * Conventions shared with the reference:
+ *   coords   int32 [N,4] = (batch, x, y, z), unique rows, 16-byte aligned      (src/spconv.h:12)
+ *   features [N,C] row-major, fp16 / bf16 / fp32 (the reference is fp16-only; dtype is a parameter here)
+ *   weights  [Co,27,Ci] = checkpoint weight [Co,3,3,3,Ci] viewed flat, tap v = kx*9 + ky*3 + kz with kx
+ *            applied to coords column 1                                           (src/spconv.h:15)
+ *   nbr      uint32 [N,27], 0xffffffff = absent; gray int32 [N] 27-bit presence mask (src/spconv.h:8)
+ */
+#ifndef T2SC_H_
+#define T2SC_H_
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct t2sc_ctx t2sc_ctx;
+typedef struct t2sc_plan t2sc_plan;
+
+/* dtype codes: same numeric values as the reference's `enum DT` (src/core.h:22) for the float types */
+enum { T2SC_F32 = 0, T2SC_F16 = 1, T2SC_BF16 = 2, T2SC_U8 = 5 };
+/* activations: the reference's `enum Act` (src/ops.h:11) shifted by one so that 0 means none */
+enum { T2SC_ACT_NONE = 0, T2SC_ACT_SILU = 1, T2SC_ACT_GELU_TANH = 2, T2SC_ACT_GELU_ERF = 3 };
+/* status codes */
+enum { T2SC_OK = 0, T2SC_ERR_ARG = -1, T2SC_ERR_CUDA = -2, T2SC_ERR_UNSUPPORTED = -3, T2SC_ERR_DEVICE = -4 };
+/* conv kernel variants (t2sc_subm_conv `variant`): AUTO picks tcgen05 whenever the shape allows it */
+enum { T2SC_VARIANT_AUTO = 0, T2SC_VARIANT_SIMT = 1, T2SC_VARIANT_UMMA = 2 };
+
+/* ---- context.  Replaces the reference's process-wide stream and allocator (src/core.cu:20-40):
+ * one context per device; `stream` is a cudaStream_t (NULL = the context creates its own
+ * non-blocking stream).  Scratch (hash table, sort buffers, plans) comes from the device's
+ * stream-ordered memory pool, as in the reference. */
+int t2sc_ctx_create(int device, void* stream, t2sc_ctx** out);
+int t2sc_ctx_destroy(t2sc_ctx* ctx);
+int t2sc_ctx_sync(t2sc_ctx* ctx);                      /* replaces dsync(), src/core.cu:29 */
+const char* t2sc_last_error(const t2sc_ctx* ctx);      /* ctx may be NULL: error of the last failed create */
+int64_t t2sc_launch_count(const t2sc_ctx* ctx);        /* kernels of this library launched so far */
+int t2sc_device_status(t2sc_ctx* ctx, int* status_host); /* syncs; non-zero = a bounded device-side wait gave up */
+
+/* ---- neighbour maps.  Replaces build_neighbors (src/spconv.cu:38-54; kernels :14-36).
+ * Writes nbr [n,27], gray [n] and, when `sorted` is not NULL, the reference's row order: the stable
+ * ascending argsort of the gray->binary key (src/spconv.cu:34,47-52).  Duplicate coordinates resolve to
+ * the lowest row index (the reference leaves it to a race).  n = 0 returns at once. */
+int t2sc_build_neighbors(t2sc_ctx* ctx, const int32_t* coords, int64_t n, int W, int H, int D,
+                         uint32_t* nbr, int32_t* gray, int32_t* sorted);
+
+/* Replaces SpConvCache::valid (src/spconv.cu:56-75).  seg [ceil(n/B1)+1] exclusive offsets, list
+ * [27*ceil(n/B1)] ascending taps present in each block of B1 consecutive `sorted` rows; *total_host
+ * receives seg[nb] (one host sync, as in the reference). */
+int t2sc_valid_taps(t2sc_ctx* ctx, const int32_t* gray, const int32_t* sorted, int64_t n, int B1,
+                    int32_t* seg, int32_t* list, int64_t* total_host);
+
+/* ---- 2x subdivision maps.  Replaces SDecoder::c2s (src/sdec.cu:45-57; kernels :21-33).
+ * `sub` is [n,8]: fp16 logits (kept iff > 0, T2SC_F16), bf16 logits (T2SC_BF16) or uint8 flags (kept iff
+ * non-zero, T2SC_U8).  count: off [n+1] exclusive child offsets, *m_host = number of children (one host
+ * sync, as in the reference).  emit: child_coords [m,4] and src [m] = parent*8 + slot, (parent,slot)
+ * ascending, child = (b, 2x+(s&1), 2y+(s>>1&1), 2z+(s>>2&1)). */
+int t2sc_subdivide_count(t2sc_ctx* ctx, const void* sub, int sub_dtype, int64_t n, int32_t* off, int64_t* m_host);
+int t2sc_subdivide_emit(t2sc_ctx* ctx, const void* sub, int sub_dtype, const int32_t* coords, const int32_t* off,
+                        int64_t n, int32_t* child_coords, int32_t* src);
+
+/* Replaces k_gather_rows (src/sdec.cu:34-37): y[r,:] = x.view(-1,C)[src[r],:]. */
+int t2sc_gather_rows(t2sc_ctx* ctx, const void* x, const int32_t* src, int64_t m, int C, int dtype, void* y);
+/* Replaces k_add_skip (src/sdec.cu:39-43): h[r,c] += x[src[r]>>3, (src[r]&7)*(Cin/8) + c/rep]. */
+int t2sc_add_skip(t2sc_ctx* ctx, void* h, const void* x, const int32_t* src, int64_t m, int Co, int Cin, int rep, int dtype);
+
+/* ---- execution plan for one neighbour map (replaces the scheduling half of SpConvCache: `sorted`
+ * and valid(), src/spconv.h:6-11).  Orders the output rows so that rows of one 128-row tile share
+ * most taps, and records each tile's tap mask.  `src` = NULL plans a submanifold conv over the n_rows
+ * rows of nbr/gray; src [m] (from t2sc_subdivide_emit) plans the 2x-subdivision conv: m child rows,
+ * each using its parent's neighbour row and the weight rows of its slot.  block_rows > 0 keeps the
+ * ordering local to runs of that many caller rows (cache locality on large maps); 0 = library default.
+ * The plan borrows nbr and src: they must outlive it. */
+int t2sc_plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_t* gray, int64_t n_rows,
+                     const int32_t* src, int64_t m, int64_t block_rows, t2sc_plan** out);
+int t2sc_plan_destroy(t2sc_ctx* ctx, t2sc_plan* plan);
+/* tiles, sum over tiles of rows*popcount(tile mask), sum over rows of popcount(row mask) (syncs) */
+int t2sc_plan_stats(t2sc_ctx* ctx, t2sc_plan* plan, int64_t* tiles, int64_t* computed_taps, int64_t* active_taps);
+/* internal row order of the plan, int32 [m] (for inspection and tests) */
+int t2sc_plan_order(t2sc_ctx* ctx, t2sc_plan* plan, int32_t* order_out);
+
+/* ---- fused epilogue, applied in this order with the reference's rounding points:
+ * round(acc) -> + bias (storage dtype, rounded; src/spconv.cu:141-143) -> LayerNorm over Co in fp32,
+ * rounded (src/ops.cu:17-76) -> activation, rounded (src/ops.cu:79-90) -> + residual, rounded
+ * (add_, src/ops.cu:105-113) -> + skip (k_add_skip, src/sdec.cu:39-43). */
+typedef struct {
+  const void* bias;        /* [Co] (subdivision conv: [8*Co]) in the feature dtype, or NULL */
+  int ln;                  /* 0 = none, 1 = LayerNorm over the Co output channels */
+  const float* ln_gamma;   /* fp32 [Co] or NULL (no affine) */
+  const float* ln_beta;    /* fp32 [Co] or NULL */
+  float ln_eps;
+  int act;                 /* T2SC_ACT_* */
+  const void* residual;    /* [n_out,Co] feature dtype or NULL */
+  const void* skip_x;      /* subdivision skip: parent features [n_parent, skip_cin] or NULL */
+  const int32_t* skip_src; /* [n_out] parent*8+slot */
+  int skip_cin, skip_rep;
+} t2sc_epilogue;
+
+/* Replaces subm_conv (src/spconv.cu:160-175; kernel :91-150) and, with a subdivision plan, the
+ * conv1 -> k_gather_rows pair of SDecoder::up (src/sdec.cu:76-80) computing kept children only.
+ * x [n_in,Ci], w [w_rows,27,Ci] (w_rows = Co, or 8*Co for a subdivision plan), y [n_out,Co] in the
+ * caller's row order; Ci % 32 == 0 as in the reference.  ep may be NULL. */
+int t2sc_subm_conv(t2sc_ctx* ctx, t2sc_plan* plan, const void* x, const void* w, const t2sc_epilogue* ep,
+                   void* y, int dtype, int64_t n_in, int Ci, int Co, int variant);
+
+/* Replaces layer_norm + act_ + add_ (src/ops.cu:17-113) as one pass over [n,C]; any of the three may
+ * be disabled (ln = 0, act = 0, residual = NULL).  In place when y == x. */
+int t2sc_row_epilogue(t2sc_ctx* ctx, const void* x, const t2sc_epilogue* ep, void* y, int64_t n, int C, int dtype);
+
+/* Whole operator with HOST buffers, as apps/parity.cu:148-167 drives it: copies coords / x / w / bias
+ * in, builds the neighbour map, runs the conv, copies y back and synchronises.  bias_host may be NULL. */
+int t2sc_subm_conv_host(t2sc_ctx* ctx, const int32_t* coords_host, int64_t n, int W, int H, int D,
+                        const void* x_host, const void* w_host, const void* bias_host, void* y_host,
+                        int dtype, int Ci, int Co);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* T2SC_H_ */

@@ -1,0 +1,286 @@
+"""GPU parity: the CUDA library (through its C ABI, via the thin Python host layer) against the CPU
+oracle on the same seeded inputs.  Integer maps must match bit for bit; features must satisfy the
+tolerance of the path's specification: max-abs <= 2e-2 and mean-rel <= 2e-3 (sum|a-b| / sum|b|) against
+an fp32-accumulated reference."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from trellis2_cuda_b200 import scenes
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS, MEAN_REL = 2e-2, 2e-3
+TD = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+
+
+@pytest.fixture(scope="module")
+def sp():
+    import trellis2_cuda_b200 as m
+    m.context()          # raises if the library or the GPU is missing
+    return m
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def host(t):
+    return t.float().cpu().numpy() if t.is_floating_point() else t.cpu().numpy()
+
+
+def check_feats(got, want, what=""):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    assert got.shape == want.shape, what
+    assert np.isfinite(got).all(), what
+    mx = np.abs(got - want).max()
+    mr = np.abs(got - want).sum() / max(np.abs(want).sum(), 1e-30)
+    assert mx <= MAX_ABS and mr <= MEAN_REL, f"{what}: max-abs {mx:.3e} mean-rel {mr:.3e}"
+
+
+def random_coords(rng, n, res, batches=1):
+    cells = rng.choice(batches * res ** 3, size=n, replace=False)
+    b, r = np.divmod(cells, res ** 3)
+    x, r = np.divmod(r, res * res)
+    y, z = np.divmod(r, res)
+    return np.stack([b, x, y, z], 1).astype(np.int32)
+
+
+def rounded(a, dt):
+    return oracle.round_to(np.asarray(a, np.float32), dt)
+
+
+# ------------------------------------------------------------------------------------------ integer maps
+@pytest.mark.parametrize("n,res,batches,ext", [(1, 4, 1, 4), (37, 4, 2, 4), (700, 10, 2, 10), (5000, 24, 1, 4096), (33, 3, 1, 3)])
+def test_neighbors_bit_exact(sp, n, res, batches, ext):
+    rng = np.random.default_rng(n)
+    c = random_coords(rng, n, res, batches)
+    nbr, gray, _, srt = oracle.build_neighbors(c, ext, ext, ext)
+    cache = sp.build_neighbors(dev(c), ext, ext, ext)
+    assert np.array_equal(host(cache.nbr).view(np.uint32), nbr)
+    assert np.array_equal(host(cache.gray), gray)
+    assert np.array_equal(host(cache.sorted), srt)
+    for B1 in (32, 128):
+        lst, seg = oracle.valid_taps(gray, srt, B1)
+        l2, s2 = cache.valid(B1)
+        assert np.array_equal(host(s2), seg)
+        assert np.array_equal(host(l2)[:len(lst)], lst)
+
+
+def test_neighbors_config1_and_empty(sp):
+    c = scenes.config1_sphere()
+    assert c.shape[0] == 14534
+    nbr, gray, _, srt = oracle.build_neighbors(c)
+    cache = sp.build_neighbors(dev(c))
+    assert np.array_equal(host(cache.nbr).view(np.uint32), nbr)
+    assert np.array_equal(host(cache.gray), gray)
+    assert np.array_equal(host(cache.sorted), srt)
+    assert int((host(cache.nbr) != -1).sum()) == 259166
+    e = sp.build_neighbors(torch.zeros((0, 4), dtype=torch.int32, device="cuda"))
+    assert e.N == 0 and e.nbr.shape == (0, 27)
+
+
+def test_neighbors_duplicates_lowest_index(sp):
+    c = np.array([[0, 1, 1, 1], [0, 1, 1, 2], [0, 1, 1, 1], [0, 1, 1, 2]], np.int32)
+    nbr, gray, _, _ = oracle.build_neighbors(c, 8, 8, 8)
+    cache = sp.build_neighbors(dev(c), 8, 8, 8)
+    assert np.array_equal(host(cache.nbr).view(np.uint32), nbr)
+    assert host(cache.nbr)[2, 13] == 0 and host(cache.nbr)[3, 13] == 1
+
+
+def test_subdivide_bit_exact(sp):
+    rng = np.random.default_rng(5)
+    c = random_coords(rng, 300, 8, 2)
+    sub = rng.standard_normal((300, 8)).astype(np.float16)
+    sub[5] = 0.0
+    sub[7] = -1.0          # a parent without children
+    cc, src = oracle.subdivide(c, sub.astype(np.float32) > 0)
+    for t in (dev(sub), dev(sub).to(torch.bfloat16), dev((sub.astype(np.float32) > 0).astype(np.uint8))):
+        lv = sp.subdivide(sp.build_neighbors(dev(c)), t)
+        assert np.array_equal(host(lv.coords), cc) and np.array_equal(host(lv.src), src)
+        nbr, gray, _, _ = oracle.build_neighbors(cc)
+        assert np.array_equal(host(lv.nb.nbr).view(np.uint32), nbr)
+    none = sp.subdivide(sp.build_neighbors(dev(c)), torch.zeros((300, 8), dtype=torch.uint8, device="cuda"))
+    assert none.coords.shape == (0, 4) and none.src.shape == (0,)
+
+
+def test_plan_is_a_permutation_with_covering_masks(sp):
+    c = scenes.config1_sphere()
+    cache = sp.build_neighbors(dev(c), block_rows=4096)
+    order = host(cache.plan.order())
+    assert np.array_equal(np.sort(order), np.arange(c.shape[0]))
+    st = cache.plan.stats()
+    assert st["tiles"] == (c.shape[0] + 127) // 128
+    assert st["active_taps"] == 259166 and st["computed_taps"] >= st["active_taps"]
+
+
+# ------------------------------------------------------------------------------------------ convolution
+def conv_case(rng, n, res, Ci, Co, dt, bias=True):
+    c = random_coords(rng, n, res)
+    x = rounded(rng.standard_normal((n, Ci)), dt)
+    w = rounded(scenes.kaiming_uniform_weight(Co, Ci, 3), dt)
+    b = rounded(0.1 * rng.standard_normal(Co), dt) if bias else None
+    return c, x, w, b
+
+
+@pytest.mark.parametrize("variant,dt,n,res,Ci,Co", [
+    ("simt", "f32", 500, 9, 32, 48), ("simt", "f16", 777, 10, 64, 64), ("simt", "bf16", 300, 8, 96, 20),
+    ("umma", "bf16", 1, 4, 64, 64), ("umma", "bf16", 130, 6, 64, 64), ("umma", "f16", 777, 10, 64, 64),
+    ("umma", "bf16", 900, 11, 128, 128), ("umma", "f16", 640, 9, 128, 256), ("umma", "bf16", 1500, 13, 256, 256),
+    ("umma", "bf16", 520, 9, 64, 512), ("umma", "f16", 400, 9, 192, 96), ("umma", "bf16", 3000, 16, 64, 32),
+])
+def test_subm_conv_matches_oracle(sp, variant, dt, n, res, Ci, Co):
+    rng = np.random.default_rng(n + Ci)
+    c, x, w, b = conv_case(rng, n, res, Ci, Co, dt)
+    nbr = oracle.build_neighbors(c)[0]
+    want = oracle.conv_block(x, w, b, nbr, dt)
+    cache = sp.build_neighbors(dev(c))
+    y = sp.subm_conv(dev(x, TD[dt]), dev(w, TD[dt]), dev(b, TD[dt]), cache, variant=variant)
+    cache.ctx.device_status()
+    check_feats(host(y), want, f"{variant} {dt} {n} {Ci}->{Co}")
+
+
+def test_subm_conv_config1_fp32(sp):
+    """Configuration 1 as specified: fp32 features, 64 -> 64, zero bias, sphere shell."""
+    c = scenes.config1_sphere()
+    x = scenes.features(c.shape[0], 64, 0)
+    w = scenes.kaiming_uniform_weight(64, 64, 1)
+    nbr = oracle.build_neighbors(c)[0]
+    want = oracle.subm_conv(x, w, None, nbr)
+    y = sp.subm_conv(dev(x), dev(w), torch.zeros(64, device="cuda"), sp.build_neighbors(dev(c)))
+    check_feats(host(y), want, "config 1")
+    assert np.abs(host(y) - want).max() < 1e-4      # fp32 in, fp32 accumulate: only summation order differs
+
+
+@pytest.mark.parametrize("variant", ["umma", "simt"])
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+def test_fused_epilogues(sp, variant, dt):
+    rng = np.random.default_rng(11)
+    Ci = Co = 64
+    c, x, w, b = conv_case(rng, 1000, 11, Ci, Co, dt)
+    g = (1.0 + 0.1 * rng.standard_normal(Co)).astype(np.float32)
+    be = (0.1 * rng.standard_normal(Co)).astype(np.float32)
+    nbr = oracle.build_neighbors(c)[0]
+    cache = sp.build_neighbors(dev(c))
+    xd, wd, bd = dev(x, TD[dt]), dev(w, TD[dt]), dev(b, TD[dt])
+    for ln, act, res in (((g, be, 1e-6), "gelu", True), ((None, None, 1e-6), "silu", False), (None, "gelu_tanh", True), (None, None, True)):
+        want = oracle.conv_block(x, w, b, nbr, dt, ln=ln, act_kind=act, residual=x if res else None)
+        lnd = None if ln is None else (None if ln[0] is None else dev(ln[0]), None if ln[1] is None else dev(ln[1]), ln[2])
+        y = sp.subm_conv(xd, wd, bd, cache, ln=lnd, act=act, residual=xd if res else None, variant=variant)
+        check_feats(host(y), want, f"{variant} {dt} ln={ln is not None} act={act} res={res}")
+    cache.ctx.device_status()
+
+
+def test_fused_layernorm_wide_falls_back_to_row_pass(sp):
+    rng = np.random.default_rng(12)
+    c, x, w, b = conv_case(rng, 600, 9, 64, 512, "bf16")
+    nbr = oracle.build_neighbors(c)[0]
+    want = oracle.conv_block(x, w, b, nbr, "bf16", ln=(None, None, 1e-6), act_kind="silu")
+    y = sp.subm_conv(dev(x, torch.bfloat16), dev(w, torch.bfloat16), dev(b, torch.bfloat16), sp.build_neighbors(dev(c)),
+                     ln=(None, None, 1e-6), act="silu")
+    check_feats(host(y), want, "Co=512 LN")
+
+
+@pytest.mark.parametrize("variant,dt", [("umma", "f16"), ("umma", "bf16"), ("simt", "f32")])
+def test_subdivision_conv_and_up_tail(sp, variant, dt):
+    """conv1 -> C2S for kept children only, then LN -> SiLU -> conv2 -> skip, against the unfused chain."""
+    rng = np.random.default_rng(21)
+    n, Ci, Cc = 500, 64, 32
+    c = random_coords(rng, n, 9)
+    x = rounded(rng.standard_normal((n, Ci)), dt)
+    keep = rng.random((n, 8)) < 0.45
+    w1 = rounded(scenes.kaiming_uniform_weight(8 * Cc, Ci, 4), dt)
+    b1 = rounded(0.1 * rng.standard_normal(8 * Cc), dt)
+    w2 = rounded(scenes.kaiming_uniform_weight(Cc, Cc, 5), dt)
+    b2 = rounded(0.1 * rng.standard_normal(Cc), dt)
+    # oracle: full conv1 then gather (the reference's order of operations)
+    nbr = oracle.build_neighbors(c)[0]
+    cc, src = oracle.subdivide(c, keep)
+    h_full = oracle.conv_block(x, w1, b1, nbr, dt)
+    hc = oracle.gather_rows(h_full, src, Cc)
+    h = oracle.round_to(oracle.layer_norm(hc, None, None, 1e-6), dt)
+    h = oracle.round_to(oracle.act(h, "silu"), dt)
+    nbr_c = oracle.build_neighbors(cc)[0]
+    rep = Cc // (Ci // 8)
+    want = oracle.conv_block(h, w2, b2, nbr_c, dt, skip=(x, src, rep))
+    # library: fused
+    parent = sp.build_neighbors(dev(c))
+    lv = sp.subdivide(parent, dev(keep.astype(np.uint8)))
+    assert np.array_equal(host(lv.src), src)
+    xd = dev(x, TD[dt])
+    hc_d = sp.subdiv_conv(xd, dev(w1, TD[dt]), dev(b1, TD[dt]), lv, variant=variant)
+    check_feats(host(hc_d), hc, "subdivision conv")
+    h_d = sp.subdiv_conv(xd, dev(w1, TD[dt]), dev(b1, TD[dt]), lv, ln=(None, None, 1e-6), act="silu", variant=variant)
+    check_feats(host(h_d), h, "subdivision conv + LN + SiLU")
+    out = sp.subm_conv(h_d, dev(w2, TD[dt]), dev(b2, TD[dt]), lv.nb, skip=(xd, lv.src, rep), variant=variant)
+    check_feats(host(out), want, "up-block tail")
+    # the unfused operators give the same rows
+    g = sp.gather_rows(dev(h_full, TD[dt]), lv.src, Cc)
+    assert np.array_equal(host(g), hc)
+    parent.ctx.device_status()
+
+
+def test_row_ops(sp):
+    rng = np.random.default_rng(31)
+    for dt in ("f32", "f16", "bf16"):
+        x = rounded(rng.standard_normal((257, 96)) * 2 + 0.5, dt)
+        r = rounded(rng.standard_normal((257, 96)), dt)
+        g = rng.standard_normal(96).astype(np.float32)
+        b = rng.standard_normal(96).astype(np.float32)
+        want = oracle.round_to(oracle.layer_norm(x, g, b, 1e-5), dt)
+        got = host(sp.layer_norm(dev(x, TD[dt]), dev(g), dev(b), 1e-5))
+        check_feats(got, want, f"layer_norm {dt}")
+        for kind in ("silu", "gelu", "gelu_tanh"):
+            want = oracle.round_to(oracle.act(x, kind), dt)
+            got = host(sp.act_(dev(x, TD[dt]), kind))
+            check_feats(got, want, f"{kind} {dt}")
+        got = host(sp.add_(dev(x, TD[dt]), dev(r, TD[dt])))
+        assert np.array_equal(got, oracle.round_to(x + r, dt))
+
+
+def test_host_buffer_entry_point(sp):
+    rng = np.random.default_rng(41)
+    c, x, w, b = conv_case(rng, 2000, 14, 64, 64, "bf16")
+    want = oracle.conv_block(x, w, b, oracle.build_neighbors(c)[0], "bf16")
+    t = lambda a: torch.from_numpy(a).to(torch.bfloat16).pin_memory()
+    y = sp.subm_conv_host(torch.from_numpy(c).pin_memory(), t(x), t(w), t(b))
+    check_feats(y.float().numpy(), want, "host entry")
+
+
+def test_errors_are_reported_not_thrown_across_the_abi(sp):
+    c = dev(random_coords(np.random.default_rng(0), 50, 5))
+    cache = sp.build_neighbors(c)
+    x = torch.zeros((50, 48), device="cuda", dtype=torch.float16)          # Ci % 32 != 0
+    w = torch.zeros((64, 27, 48), device="cuda", dtype=torch.float16)
+    with pytest.raises(sp.T2scError, match="Ci"):
+        sp.subm_conv(x, w, None, cache)
+    with pytest.raises(sp.T2scError, match="rows"):
+        sp.subm_conv(torch.zeros((49, 64), device="cuda", dtype=torch.float16), torch.zeros((64, 27, 64), device="cuda", dtype=torch.float16), None, cache)
+    with pytest.raises(sp.T2scError, match="tcgen05"):
+        sp.subm_conv(torch.zeros((50, 64), device="cuda"), torch.zeros((64, 27, 64), device="cuda"), None, cache, variant="umma")
+
+
+# ------------------------------------------------------------------------------------------ full-size properties
+def test_config2_properties_at_full_size(sp):
+    """Configuration 2 (217,821 voxels, 256 -> 256, bf16): sampled rows against the oracle, plus
+    size-independent properties: homogeneity in the weights by a power of two is exact, zero features give
+    zero, and the two kernel variants agree."""
+    c = scenes.config2_shell()
+    n, C = c.shape[0], 256
+    x = torch.from_numpy(scenes.features(n, C, 0)).cuda().to(torch.bfloat16)
+    w = torch.from_numpy(scenes.kaiming_uniform_weight(C, C, 1)).cuda().to(torch.bfloat16)
+    cache = sp.build_neighbors(dev(c))
+    nbr, gray, _, srt = oracle.build_neighbors(c)
+    assert np.array_equal(host(cache.nbr).view(np.uint32), nbr) and np.array_equal(host(cache.sorted), srt)
+    y = sp.subm_conv(x, w, None, cache)
+    cache.ctx.device_status()
+    rows = np.random.default_rng(0).choice(n, 400, replace=False).astype(np.int32)
+    want = oracle.round_to(oracle.subm_conv(host(x), host(w), None, nbr, nrow=rows), "bf16")
+    check_feats(host(y)[rows], want, "config 2 sample")
+    y2 = sp.subm_conv(x, w * 2, None, cache)
+    assert torch.equal(y2.float(), y.float() * 2)
+    assert torch.count_nonzero(sp.subm_conv(torch.zeros_like(x), w, None, cache)) == 0
+    ys = sp.subm_conv(x, w, None, cache, variant="simt")
+    check_feats(host(ys)[::97], host(y)[::97], "variants agree")

@@ -1,0 +1,164 @@
+// C-ABI entry points that are not kernels themselves: context, errors, conv dispatch, host-buffer call.
+#include "common.cuh"
+
+static char g_create_err[512] = {0};
+
+int t2sc_fail(t2sc_ctx* ctx, int code, const char* fmt, ...) {
+  char* dst = ctx ? ctx->err : g_create_err;
+  size_t cap = ctx ? sizeof(ctx->err) : sizeof(g_create_err);
+  va_list a; va_start(a, fmt); vsnprintf(dst, cap, fmt, a); va_end(a);
+  return code;
+}
+
+extern "C" const char* t2sc_last_error(const t2sc_ctx* ctx) { return ctx ? ctx->err : g_create_err; }
+extern "C" int64_t t2sc_launch_count(const t2sc_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+extern "C" int t2sc_ctx_create(int device, void* stream, t2sc_ctx** out) {
+  if (!out) return t2sc_fail(nullptr, T2SC_ERR_ARG, "t2sc_ctx_create: out is NULL");
+  *out = nullptr;
+  int ndev = 0;
+  cudaError_t e = cudaGetDeviceCount(&ndev);
+  if (e != cudaSuccess || ndev == 0)
+    return t2sc_fail(nullptr, T2SC_ERR_CUDA, "t2sc_ctx_create: no CUDA device (%s); this library has no CPU path",
+                     cudaGetErrorString(e));
+  if (device < 0 || device >= ndev) return t2sc_fail(nullptr, T2SC_ERR_ARG, "t2sc_ctx_create: device %d of %d", device, ndev);
+  cudaDeviceProp prop;
+  if ((e = cudaSetDevice(device)) != cudaSuccess || (e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess)
+    return t2sc_fail(nullptr, T2SC_ERR_CUDA, "t2sc_ctx_create: %s", cudaGetErrorString(e));
+  if (prop.major != 10)
+    return t2sc_fail(nullptr, T2SC_ERR_UNSUPPORTED, "t2sc_ctx_create: device %d is sm_%d%d; this library is built for sm_100a only",
+                     device, prop.major, prop.minor);
+  t2sc_ctx* c = new t2sc_ctx();
+  c->device = device; c->num_sms = prop.multiProcessorCount; c->smem_optin = (int)prop.sharedMemPerBlockOptin;
+  if (stream) { c->stream = (cudaStream_t)stream; c->own_stream = false; }
+  else {
+    if ((e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking)) != cudaSuccess) {
+      delete c; return t2sc_fail(nullptr, T2SC_ERR_CUDA, "t2sc_ctx_create: %s", cudaGetErrorString(e));
+    }
+    c->own_stream = true;
+  }
+  // keep freed scratch in the pool instead of returning it to the driver at every sync (src/core.cu:24-26 does the same)
+  cudaMemPool_t pool;
+  if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
+    uint64_t thr = UINT64_MAX; cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &thr);
+  }
+  if ((e = cudaMalloc(&c->status, sizeof(int))) != cudaSuccess || (e = cudaMemset(c->status, 0, sizeof(int))) != cudaSuccess) {
+    if (c->own_stream) cudaStreamDestroy(c->stream);
+    delete c; return t2sc_fail(nullptr, T2SC_ERR_CUDA, "t2sc_ctx_create: %s", cudaGetErrorString(e));
+  }
+  *out = c;
+  return T2SC_OK;
+}
+
+extern "C" int t2sc_ctx_destroy(t2sc_ctx* ctx) {
+  if (!ctx) return T2SC_OK;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  cudaFree(ctx->status);
+  if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
+  delete ctx;
+  return T2SC_OK;
+}
+
+extern "C" int t2sc_ctx_sync(t2sc_ctx* ctx) {
+  T2_REQ(ctx, ctx != nullptr, "null context");
+  T2_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return T2SC_OK;
+}
+
+extern "C" int t2sc_device_status(t2sc_ctx* ctx, int* status_host) {
+  T2_REQ(ctx, ctx && status_host, "null argument");
+  T2_CUDA(ctx, cudaMemcpyAsync(status_host, ctx->status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+  T2_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (*status_host) {
+    T2_CUDA(ctx, cudaMemsetAsync(ctx->status, 0, sizeof(int), ctx->stream));
+    return t2sc_fail(ctx, T2SC_ERR_DEVICE, "a device-side wait gave up (status word 0x%x); results of the last launches are invalid", *status_host);
+  }
+  return T2SC_OK;
+}
+
+// ------------------------------------------------------------------------------------------ conv dispatch
+extern "C" int t2sc_subm_conv(t2sc_ctx* ctx, t2sc_plan* plan, const void* x, const void* w, const t2sc_epilogue* ep,
+                              void* y, int dtype, int64_t n_in, int Ci, int Co, int variant) {
+  T2_REQ(ctx, ctx && plan, "null context or plan");
+  T2_REQ(ctx, dtype == T2SC_F32 || dtype == T2SC_F16 || dtype == T2SC_BF16, "dtype %d", dtype);
+  T2_REQ(ctx, Ci > 0 && Co > 0 && Ci % 32 == 0, "spconv shapes Ci=%d Co=%d (Ci must be a multiple of 32)", Ci, Co);
+  T2_REQ(ctx, n_in >= 0 && n_in < (1ll << 31), "n_in=%lld", (long long)n_in);
+  if (plan->n_out == 0) return T2SC_OK;
+  T2_REQ(ctx, x && w && y, "null tensor");
+  T2_REQ(ctx, ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((uintptr_t)y % 16 == 0), "x, w, y must be 16-byte aligned");
+  EpiDev e = epi_dev(ep);
+  if (e.skip_x) T2_REQ(ctx, e.skip_src && e.skip_cin % 8 == 0 && e.skip_rep > 0 && Co == (e.skip_cin / 8) * e.skip_rep,
+                       "skip: Co=%d Cin=%d rep=%d", Co, e.skip_cin, e.skip_rep);
+  i64 w_rows = plan->src ? 8ll * Co : Co;
+  bool umma_ok = conv_umma_supported(dtype, Ci, Co, e);
+  if (variant == T2SC_VARIANT_UMMA && !umma_ok)
+    return t2sc_fail(ctx, T2SC_ERR_UNSUPPORTED, "tcgen05 variant needs fp16/bf16, Ci %% 64 == 0, Co %% 32 == 0 (Ci=%d Co=%d dtype=%d)", Ci, Co, dtype);
+  bool use_umma = variant == T2SC_VARIANT_UMMA || (variant == T2SC_VARIANT_AUTO && umma_ok);
+  // LayerNorm needs the whole output row in one CTA: fused on the tcgen05 path for Co <= 256, else a second pass
+  bool fuse_all = use_umma && (!e.ln || Co <= 256);
+  if (fuse_all) return conv_umma_launch(ctx, plan, x, w, w_rows, e, y, dtype, n_in, Ci, Co);
+  EpiDev first = e, rest = e;
+  if (e.ln) {  // conv + bias now; LN -> act -> residual -> skip in the row pass
+    first.ln = 0; first.act = 0; first.residual = nullptr; first.skip_x = nullptr; first.gamma = first.beta = nullptr;
+    rest.bias = nullptr;
+  }
+  int rc = use_umma ? conv_umma_launch(ctx, plan, x, w, w_rows, first, y, dtype, n_in, Ci, Co)
+                    : conv_simt_launch(ctx, plan, x, w, first, y, dtype, Ci, Co);
+  if (rc != T2SC_OK || !e.ln) return rc;
+  return row_epilogue_launch(ctx, y, rest, y, plan->n_out, Co, dtype);
+}
+
+extern "C" int t2sc_row_epilogue(t2sc_ctx* ctx, const void* x, const t2sc_epilogue* ep, void* y, int64_t n, int C, int dtype) {
+  T2_REQ(ctx, ctx != nullptr, "null context");
+  T2_REQ(ctx, dtype == T2SC_F32 || dtype == T2SC_F16 || dtype == T2SC_BF16, "dtype %d", dtype);
+  T2_REQ(ctx, n >= 0 && C > 0 && C % 4 == 0, "n=%lld C=%d (C must be a multiple of 4)", (long long)n, C);
+  if (n == 0) return T2SC_OK;
+  T2_REQ(ctx, x && y, "null tensor");
+  return row_epilogue_launch(ctx, x, epi_dev(ep), y, n, C, dtype);
+}
+
+// ------------------------------------------------------------------------------------------ host-buffer operator
+extern "C" int t2sc_subm_conv_host(t2sc_ctx* ctx, const int32_t* coords_host, int64_t n, int W, int H, int D,
+                                   const void* x_host, const void* w_host, const void* bias_host, void* y_host,
+                                   int dtype, int Ci, int Co) {
+  T2_REQ(ctx, ctx != nullptr, "null context");
+  T2_REQ(ctx, n >= 0 && n < (1ll << 31), "n=%lld", (long long)n);
+  if (n == 0) return T2SC_OK;
+  T2_REQ(ctx, coords_host && x_host && w_host && y_host, "null host buffer");
+  T2_REQ(ctx, dtype == T2SC_F32 || dtype == T2SC_F16 || dtype == T2SC_BF16, "dtype %d", dtype);
+  size_t es = dtype_size(dtype);
+  int32_t* coords = nullptr; uint32_t* nbr = nullptr; int32_t* gray = nullptr;
+  char *x = nullptr, *w = nullptr, *b = nullptr, *y = nullptr;
+  t2sc_plan* plan = nullptr;
+  int rc = T2SC_OK;
+  auto cleanup = [&]() {
+    if (plan) t2sc_plan_destroy(ctx, plan);
+    t2_free(ctx, coords); t2_free(ctx, nbr); t2_free(ctx, gray); t2_free(ctx, x); t2_free(ctx, w); t2_free(ctx, b); t2_free(ctx, y);
+  };
+#define HOST_TRY(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) { cleanup(); return t2sc_fail(ctx, T2SC_ERR_CUDA, "CUDA %s: %s", #call, cudaGetErrorString(e_)); } } while (0)
+  HOST_TRY(cudaSetDevice(ctx->device));
+  HOST_TRY(t2_alloc(ctx, &coords, (size_t)n * 4));
+  HOST_TRY(t2_alloc(ctx, &nbr, (size_t)n * 27));
+  HOST_TRY(t2_alloc(ctx, &gray, (size_t)n));
+  HOST_TRY(t2_alloc(ctx, &x, (size_t)n * Ci * es));
+  HOST_TRY(t2_alloc(ctx, &w, (size_t)Co * 27 * Ci * es));
+  HOST_TRY(t2_alloc(ctx, &y, (size_t)n * Co * es));
+  HOST_TRY(cudaMemcpyAsync(coords, coords_host, (size_t)n * 16, cudaMemcpyHostToDevice, ctx->stream));
+  HOST_TRY(cudaMemcpyAsync(x, x_host, (size_t)n * Ci * es, cudaMemcpyHostToDevice, ctx->stream));
+  HOST_TRY(cudaMemcpyAsync(w, w_host, (size_t)Co * 27 * Ci * es, cudaMemcpyHostToDevice, ctx->stream));
+  if (bias_host) {
+    HOST_TRY(t2_alloc(ctx, &b, (size_t)Co * es));
+    HOST_TRY(cudaMemcpyAsync(b, bias_host, (size_t)Co * es, cudaMemcpyHostToDevice, ctx->stream));
+  }
+  if ((rc = t2sc_build_neighbors(ctx, coords, n, W, H, D, nbr, gray, nullptr)) != T2SC_OK) { cleanup(); return rc; }
+  if ((rc = t2sc_plan_create(ctx, nbr, gray, n, nullptr, n, 0, &plan)) != T2SC_OK) { cleanup(); return rc; }
+  t2sc_epilogue ep; memset(&ep, 0, sizeof(ep)); ep.bias = b;
+  if ((rc = t2sc_subm_conv(ctx, plan, x, w, &ep, y, dtype, n, Ci, Co, T2SC_VARIANT_AUTO)) != T2SC_OK) { cleanup(); return rc; }
+  HOST_TRY(cudaMemcpyAsync(y_host, y, (size_t)n * Co * es, cudaMemcpyDeviceToHost, ctx->stream));
+  HOST_TRY(cudaStreamSynchronize(ctx->stream));
+#undef HOST_TRY
+  cleanup();
+  int st = 0;
+  return t2sc_device_status(ctx, &st);
+}

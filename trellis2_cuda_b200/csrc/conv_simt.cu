@@ -1,0 +1,184 @@
+// CUDA-core variant of the masked implicit-GEMM sparse conv: fp32 math on fp32 / fp16 / bf16 storage.
+//
+// This is the path for fp32 features (the tensor cores would drop them to tf32) and for shapes the
+// tcgen05 kernel does not take (Ci not a multiple of 64, Co not a multiple of 32).  It computes the
+// operator of src/spconv.cu:91-150 (trellis2-cuda): y[i,co] = sum over the tile's taps, ascending, of
+// x[nbr[i,v],:] . w[co,v,:], fp32 accumulation, absent neighbours contributing zeros.
+// One CTA = one 128-row plan tile x 64 output channels; 256 threads, 8x4 outputs each; K in chunks of 16.
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 64, BK = 16, LDA = BM + 4, LDB = BN + 4;
+
+template <class T> __device__ __forceinline__ void load8(const T* p, float* o);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float* o) {
+  float4 a = __ldg((const float4*)p), b = __ldg((const float4*)p + 1);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<__half>(const __half* p, float* o) {
+  uint4 r = __ldg((const uint4*)p); const __half2* h = (const __half2*)&r;
+#pragma unroll
+  for (int i = 0; i < 4; i++) { float2 f = __half22float2(h[i]); o[2 * i] = f.x; o[2 * i + 1] = f.y; }
+}
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* o) {
+  uint4 r = __ldg((const uint4*)p); const __nv_bfloat162* h = (const __nv_bfloat162*)&r;
+#pragma unroll
+  for (int i = 0; i < 4; i++) { float2 f = __bfloat1622float2(h[i]); o[2 * i] = f.x; o[2 * i + 1] = f.y; }
+}
+template <class T> __device__ __forceinline__ void load4(const T* p, float* o) {
+#pragma unroll
+  for (int i = 0; i < 4; i++) o[i] = to_f<T>(p[i]);
+}
+
+template <class T>
+__global__ void __launch_bounds__(256) k_conv_simt(const T* __restrict__ x, const T* __restrict__ w, const uint32_t* __restrict__ nbr,
+                                                   const int* __restrict__ order, const int* __restrict__ src,
+                                                   const PlanTile* __restrict__ tiles, const int* __restrict__ ntiles,
+                                                   EpiDev ep, T* __restrict__ y, int Ci, int Co) {
+  if ((int)blockIdx.x >= *ntiles) return;
+  __shared__ __align__(16) float As[BK][LDA];
+  __shared__ __align__(16) float Bs[BK][LDB];
+  __shared__ int s_out[BM];
+  __shared__ int s_nrow[BM];
+  const PlanTile tile = tiles[blockIdx.x];
+  const int tid = threadIdx.x, co0 = blockIdx.y * BN;
+  const i64 wrow0 = (i64)tile.wbase * Co;
+  if (tid < BM) {
+    int r = tid < tile.rows ? order[tile.start + tid] : -1;
+    s_out[tid] = r;
+    s_nrow[tid] = r < 0 ? -1 : (src ? (src[r] >> 3) : r);
+  }
+  __syncthreads();
+  const int ty = tid >> 4, tx = tid & 15;
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+
+  const int a_row = tid >> 1, a_k0 = (tid & 1) * 8;     // A loader: 128 rows x 2 halves of 8 channels
+  const int b_co = tid >> 2, b_k0 = (tid & 3) * 4;      // B loader: 64 channels x 4 quarters of 4 channels
+  const int a_nrow = s_nrow[a_row];
+  const int b_cog = co0 + b_co;
+
+  for (uint32_t mk = tile.mask; mk; mk &= mk - 1) {
+    const int v = __ffs(mk) - 1;
+    uint32_t a_src = a_nrow < 0 ? NBR_EMPTY : __ldg(nbr + (i64)a_nrow * 27 + v);
+    for (int c0 = 0; c0 < Ci; c0 += BK) {
+      float av[8], bv[4];
+      if (a_src != NBR_EMPTY) load8<T>(x + (i64)a_src * Ci + c0 + a_k0, av);
+      else {
+#pragma unroll
+        for (int i = 0; i < 8; i++) av[i] = 0.f;
+      }
+      if (b_cog < Co) load4<T>(w + ((wrow0 + b_cog) * 27 + v) * Ci + c0 + b_k0, bv);
+      else {
+#pragma unroll
+        for (int i = 0; i < 4; i++) bv[i] = 0.f;
+      }
+      __syncthreads();   // previous chunk fully consumed
+#pragma unroll
+      for (int i = 0; i < 8; i++) As[a_k0 + i][a_row] = av[i];
+#pragma unroll
+      for (int i = 0; i < 4; i++) Bs[b_k0 + i][b_co] = bv[i];
+      __syncthreads();
+#pragma unroll
+      for (int k = 0; k < BK; k++) {
+        float4 a0 = *(const float4*)&As[k][ty * 8], a1 = *(const float4*)&As[k][ty * 8 + 4];
+        float4 b = *(const float4*)&Bs[k][tx * 4];
+        float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        float bb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+#pragma unroll
+          for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], bb[j], acc[i][j]);
+      }
+    }
+  }
+  // epilogue: every step rounds to the storage dtype, as the unfused kernels of the reference do
+  const T* bias = (const T*)ep.bias; const T* res = (const T*)ep.residual; const T* skx = (const T*)ep.skip_x;
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    int orow = s_out[ty * 8 + i];
+    if (orow < 0) continue;
+    int sp = 0, ss = 0;
+    if (skx) { int s = ep.skip_src[orow]; sp = s >> 3; ss = s & 7; }
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      int co = co0 + tx * 4 + j;
+      if (co >= Co) continue;
+      float h = rnd<T>(acc[i][j]);
+      if (bias) h = rnd<T>(h + to_f<T>(bias[wrow0 + co]));
+      if (ep.act) h = rnd<T>(act_apply(h, ep.act));
+      if (res) h = rnd<T>(h + to_f<T>(res[(i64)orow * Co + co]));
+      if (skx) h = rnd<T>(h + to_f<T>(skx[(i64)sp * ep.skip_cin + ss * (ep.skip_cin / 8) + co / ep.skip_rep]));
+      y[(i64)orow * Co + co] = from_f<T>(h);
+    }
+  }
+}
+
+// ---- LayerNorm -> activation -> residual -> skip over [n,C], one warp per row, fp32 statistics
+template <class T>
+__global__ void __launch_bounds__(256) k_row_epilogue(const T* x, EpiDev ep, T* y, i64 n, int C) {   // y may alias x
+  i64 row = (blockIdx.x * (i64)blockDim.x + threadIdx.x) >> 5; int lane = threadIdx.x & 31;
+  if (row >= n) return;
+  const T* xr = x + row * C; T* yr = y + row * C;
+  const T* bias = (const T*)ep.bias; const T* res = (const T*)ep.residual; const T* skx = (const T*)ep.skip_x;
+  float mean = 0.f, rstd = 1.f;
+  if (ep.ln) {
+    float s = 0.f;
+    for (int c = lane; c < C; c += 32) { float v = to_f<T>(xr[c]); if (bias) v = rnd<T>(v + to_f<T>(bias[c])); s += v; }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    mean = s / (float)C;
+    float q = 0.f;
+    for (int c = lane; c < C; c += 32) { float v = to_f<T>(xr[c]); if (bias) v = rnd<T>(v + to_f<T>(bias[c])); float d = v - mean; q += d * d; }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+    rstd = rsqrtf(q / (float)C + ep.eps);
+  }
+  int sp = 0, ss = 0;
+  if (skx) { int s = ep.skip_src[row]; sp = s >> 3; ss = s & 7; }
+  for (int c = lane; c < C; c += 32) {
+    float h = to_f<T>(xr[c]);
+    if (bias) h = rnd<T>(h + to_f<T>(bias[c]));
+    if (ep.ln) {
+      float v = rstd * (h - mean);
+      if (ep.gamma) v = ep.gamma[c] * v;
+      if (ep.beta) v = v + ep.beta[c];
+      h = rnd<T>(v);
+    }
+    if (ep.act) h = rnd<T>(act_apply(h, ep.act));
+    if (res) h = rnd<T>(h + to_f<T>(res[row * C + c]));
+    if (skx) h = rnd<T>(h + to_f<T>(skx[(i64)sp * ep.skip_cin + ss * (ep.skip_cin / 8) + c / ep.skip_rep]));
+    yr[c] = from_f<T>(h);
+  }
+}
+
+}  // namespace
+
+int conv_simt_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const void* w, const EpiDev& ep, void* y,
+                     int dtype, int Ci, int Co) {
+  T2_REQ(ctx, Ci % BK == 0, "Ci=%d", Ci);
+  T2_CUDA(ctx, cudaSetDevice(ctx->device));
+  dim3 grid((unsigned)plan->max_tiles, (unsigned)cdiv_i(Co, BN));
+  if (dtype == T2SC_F32)
+    k_conv_simt<float><<<grid, 256, 0, ctx->stream>>>((const float*)x, (const float*)w, plan->nbr, plan->order, plan->src, plan->tiles, plan->ntiles, ep, (float*)y, Ci, Co);
+  else if (dtype == T2SC_F16)
+    k_conv_simt<__half><<<grid, 256, 0, ctx->stream>>>((const __half*)x, (const __half*)w, plan->nbr, plan->order, plan->src, plan->tiles, plan->ntiles, ep, (__half*)y, Ci, Co);
+  else
+    k_conv_simt<__nv_bfloat16><<<grid, 256, 0, ctx->stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, plan->nbr, plan->order, plan->src, plan->tiles, plan->ntiles, ep, (__nv_bfloat16*)y, Ci, Co);
+  T2_LAUNCHED(ctx);
+  return T2SC_OK;
+}
+
+int row_epilogue_launch(t2sc_ctx* ctx, const void* x, const EpiDev& ep, void* y, i64 n, int C, int dtype) {
+  T2_CUDA(ctx, cudaSetDevice(ctx->device));
+  int grid = cdiv_i(n * 32, 256);
+  if (dtype == T2SC_F32) k_row_epilogue<float><<<grid, 256, 0, ctx->stream>>>((const float*)x, ep, (float*)y, n, C);
+  else if (dtype == T2SC_F16) k_row_epilogue<__half><<<grid, 256, 0, ctx->stream>>>((const __half*)x, ep, (__half*)y, n, C);
+  else k_row_epilogue<__nv_bfloat16><<<grid, 256, 0, ctx->stream>>>((const __nv_bfloat16*)x, ep, (__nv_bfloat16*)y, n, C);
+  T2_LAUNCHED(ctx);
+  return T2SC_OK;
+}

@@ -1,0 +1,451 @@
+// tcgen05 / TMEM masked implicit-GEMM sparse convolution for sm_100a (fp16 or bf16 in, fp32 accumulate).
+//
+// Computes the operator of src/spconv.cu:91-150 (trellis2-cuda): for every output row and every tap
+// present in its tile, y[row, co] += x[nbr[row, v], :] . w[co, v, :].  The reference runs 32-64 row tiles
+// through mma.sync with register-staged copies; this kernel is organised around the Blackwell units:
+//
+//   * persistent CTAs, one per SM, walk (128-row plan tile x BN output channels) work items;
+//   * warps 0-3 gather the A operand: one 16-byte cp.async per (row, 8 channels), zero-filled for absent
+//     neighbours, written straight into the 128-byte-swizzled K-major layout tcgen05 reads.  The tile's
+//     slice of the neighbour map is staged in shared memory once per tile, not re-read per step;
+//   * warp 4 streams the B operand (the tap's [BN x 64] weight slab) with a 3-D TMA tile load from the
+//     weights in their checkpoint layout [Co,27,Ci] - no re-layout, no cluster multicast;
+//   * warp 5 issues tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM accumulators and releases smem
+//     stages / publishes accumulators with tcgen05.commit;
+//   * warps 6-9 drain the other accumulator with tcgen05.ld and apply the fused epilogue (bias, LayerNorm,
+//     activation, residual, skip) with the reference's rounding points, one thread per output row, and
+//     scatter rows back to the caller's order.
+//
+// Every mbarrier wait is bounded: a wait that runs out sets the context's status word, the CTA stops
+// blocking, drains and frees its TMEM; the host reports T2SC_ERR_DEVICE.
+#include "common.cuh"
+#include <cuda.h>
+
+namespace {
+
+constexpr int TILE_M = 128;
+constexpr int KCH = 64;                      // channels per pipeline step = one 128-byte swizzle row
+constexpr int A_BYTES = TILE_M * 128;
+constexpr int NUM_PROD_THREADS = 128;
+constexpr int WARP_TMA = 4, WARP_MMA = 5, WARP_EPI0 = 6;
+constexpr int NTHREADS = 320;
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // ~2 s at boost clock
+constexpr int SMEM_BUDGET = 227 * 1024;
+
+__host__ __device__ constexpr int stage_bytes(int BN) { return A_BYTES + BN * 128; }
+__host__ __device__ constexpr int aux_bytes() { return TILE_M * 27 * 4 + TILE_M * 4 + 256; }
+__host__ __device__ constexpr int num_stages(int BN) {
+  int s = (SMEM_BUDGET - 1024 - aux_bytes()) / stage_bytes(BN);
+  return s > 8 ? 8 : s;
+}
+
+struct ConvArgs {
+  const void* x; void* y; const uint32_t* nbr; const int* order; const int* src;
+  const PlanTile* tiles; const int* ntiles; int* status;
+  int Ci, Co, n_cot, is_bf16;
+  EpiDev ep;
+};
+
+// ------------------------------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  After any wait in the CTA has given up, all later waits return at once.
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if (mbar_try(bar, parity)) return;
+  long long t0 = clock64();
+  while (!mbar_try(bar, parity)) {
+    if (*abort_flag || clock64() - t0 > WAIT_LIMIT_CYCLES) { *abort_flag = 1; atomicOr(status, code); return; }
+  }
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+// arrive on `bar` once all cp.async issued so far by this thread have landed (pending count +1 now, -1 then)
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+               "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile, rows of 128 bytes, 128-byte swizzle: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);   // start address
+  d |= (uint64_t)1 << 16;                      // leading byte offset: unused with swizzled K-major, set to 1
+  d |= (uint64_t)(1024 >> 4) << 32;            // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                      // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                      // 128-byte swizzle
+  return d;
+}
+__host__ __device__ constexpr uint32_t umma_idesc(int N, int is_bf16) {
+  return (1u << 4)                              // D = fp32
+       | ((is_bf16 ? 1u : 0u) << 7)             // A format
+       | ((is_bf16 ? 1u : 0u) << 10)            // B format
+       | ((uint32_t)(N >> 3) << 17)             // N
+       | ((uint32_t)(TILE_M >> 4) << 24);       // M
+}
+
+template <class T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&h);
+}
+template <class T> __device__ __forceinline__ float2 unpack2(uint32_t v);
+template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t v) { return __half22float2(*reinterpret_cast<__half2*>(&v)); }
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v)); }
+
+// ------------------------------------------------------------------------------------------ kernel
+template <int BN, class T>
+__global__ void __launch_bounds__(NTHREADS, 1) k_conv_umma(const __grid_constant__ CUtensorMap tmw, const ConvArgs a) {
+  constexpr int S = num_stages(BN);
+  constexpr int STAGE = stage_bytes(BN);
+  constexpr int B_BYTES = BN * 128;
+  constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint32_t* nbr_s = (uint32_t*)(smem + S * STAGE);
+  int* nrow_s = (int*)(nbr_s + TILE_M * 27);
+  uint64_t* bars = (uint64_t*)(nrow_s + TILE_M);     // full[S] empty[S] accf[2] acce[2]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * S + 4);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * S, bar_accf = bar_empty + 8 * S, bar_acce = bar_accf + 16;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, NUM_PROD_THREADS + 1); mbar_init(bar_empty + 8 * s, 1); }
+    for (int b = 0; b < 2; b++) { mbar_init(bar_accf + 8 * b, 1); mbar_init(bar_acce + 8 * b, 128); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == WARP_MMA) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int ntiles = *a.ntiles;
+  const int nitems = ntiles * a.n_cot;
+  const int nchunk = a.Ci / KCH;
+
+  if (warp < 4) {
+    // ===================================================================== A producer (gather)
+    const T* x = (const T*)a.x;
+    const int t = threadIdx.x, jbase = t >> 3, c16 = t & 7;
+    const uint32_t dst_thread = (uint32_t)(jbase * 128 + ((c16 ^ (jbase & 7)) << 4));   // (jbase + 16 i) & 7 == jbase & 7
+    uint32_t it = 0; int cur_tile = -1;
+    for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+      const int tile_id = item / a.n_cot;
+      const PlanTile tile = a.tiles[tile_id];
+      if (tile_id != cur_tile) {
+        cur_tile = tile_id;
+        int nr = -1;
+        if (t < tile.rows) { int r = a.order[tile.start + t]; nr = a.src ? (a.src[r] >> 3) : r; }
+        nrow_s[t] = nr;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        for (int e = t; e < TILE_M * 27; e += NUM_PROD_THREADS) {
+          int j = e / 27, v = e - j * 27, r = nrow_s[j];
+          nbr_s[e] = r < 0 ? NBR_EMPTY : __ldg(a.nbr + (i64)r * 27 + v);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      for (uint32_t mk = tile.mask; mk; mk &= mk - 1) {
+        const int v = __ffs(mk) - 1;
+        uint32_t idx[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) idx[i] = nbr_s[(jbase + 16 * i) * 27 + v];
+        for (int c = 0; c < nchunk; c++, it++) {
+          const uint32_t s = it % S, ph = (it / S) & 1;
+          mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, a.status, 1);
+          const uint32_t dst = smem_base + s * STAGE + dst_thread;
+          const T* xs = x + c * KCH + c16 * 8;
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const bool present = idx[i] != NBR_EMPTY;
+            cp_async16(dst + i * (16 * 128), present ? (const void*)(xs + (i64)idx[i] * a.Ci) : (const void*)x, present ? 16u : 0u);
+          }
+          cp_async_arrive(bar_full + 8 * s);
+          mbar_arrive(bar_full + 8 * s);
+        }
+      }
+    }
+    cp_async_wait_all();
+  } else if (warp == WARP_TMA) {
+    // ===================================================================== B producer (weights by TMA)
+    uint32_t it = 0;
+    for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+      const int tile_id = item / a.n_cot, cot = item - tile_id * a.n_cot;
+      const PlanTile tile = a.tiles[tile_id];
+      const int wrow = tile.wbase * a.Co + cot * BN;
+      for (uint32_t mk = tile.mask; mk; mk &= mk - 1) {
+        const int v = __ffs(mk) - 1;
+        for (int c = 0; c < nchunk; c++, it++) {
+          const uint32_t s = it % S, ph = (it / S) & 1;
+          mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, a.status, 2);
+          if (lane == 0) {
+            mbar_arrive_expect_tx(bar_full + 8 * s, B_BYTES);
+            tma_load_3d(smem_base + s * STAGE + A_BYTES, &tmw, c * KCH, v, wrow, bar_full + 8 * s);
+          }
+          __syncwarp();
+        }
+      }
+    }
+  } else if (warp == WARP_MMA) {
+    // ===================================================================== MMA issuer
+    const uint32_t idesc = umma_idesc(BN, a.is_bf16);
+    uint32_t it = 0, acc_it = 0;
+    for (int item = blockIdx.x; item < nitems; item += gridDim.x, acc_it++) {
+      const int tile_id = item / a.n_cot;
+      const PlanTile tile = a.tiles[tile_id];
+      const uint32_t buf = acc_it & 1, aph = (acc_it >> 1) & 1;
+      mbar_wait(bar_acce + 8 * buf, aph ^ 1, abort_flag, a.status, 4);
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * BN;
+      const int ksteps = __popc(tile.mask) * nchunk;
+      for (int k = 0; k < ksteps; k++, it++) {
+        const uint32_t s = it % S, ph = (it / S) & 1;
+        mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, 8);
+        tc_fence_after();
+        if (lane == 0) {
+          const uint64_t ad = umma_desc(smem_base + s * STAGE), bd = umma_desc(smem_base + s * STAGE + A_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < KCH / 16; kk++)      // +32 bytes along K inside the swizzle row = +2 in the address field
+            tc_mma(d_tmem, ad + 2 * kk, bd + 2 * kk, idesc, (k > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(bar_empty + 8 * s);
+        }
+        __syncwarp();
+      }
+      if (lane == 0) tc_commit(bar_accf + 8 * buf);
+      __syncwarp();
+    }
+  } else {
+    // ===================================================================== epilogue
+    T* y = (T*)a.y;
+    const T* bias = (const T*)a.ep.bias; const T* res = (const T*)a.ep.residual; const T* skx = (const T*)a.ep.skip_x;
+    const int q = warp & 3, j = q * 32 + lane;
+    uint32_t acc_it = 0;
+    for (int item = blockIdx.x; item < nitems; item += gridDim.x, acc_it++) {
+      const int tile_id = item / a.n_cot, cot = item - tile_id * a.n_cot;
+      const PlanTile tile = a.tiles[tile_id];
+      const uint32_t buf = acc_it & 1, aph = (acc_it >> 1) & 1;
+      const int orow = j < tile.rows ? a.order[tile.start + j] : -1;
+      const int wcol0 = tile.wbase * a.Co + cot * BN;      // bias index of this item's first column
+      int sp = 0, ss = 0;
+      if (skx && orow >= 0) { int sv = a.ep.skip_src[orow]; sp = sv >> 3; ss = sv & 7; }
+      mbar_wait(bar_accf + 8 * buf, aph, abort_flag, a.status, 16);
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+      float mean = 0.f, rstd = 1.f;
+      if (a.ep.ln) {      // whole row lives in this accumulator (n_cot == 1): two statistics passes over TMEM
+        float sum = 0.f;
+        for (int cc = 0; cc < BN / 32; cc++) {
+          uint32_t r[32]; tc_ld32(taddr + cc * 32, r); tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; i++) {
+            float h = rnd<T>(__uint_as_float(r[i]));
+            if (bias) h = rnd<T>(h + to_f<T>(bias[wcol0 + cc * 32 + i]));
+            sum += h;
+          }
+        }
+        mean = sum / (float)BN;
+        float qs = 0.f;
+        for (int cc = 0; cc < BN / 32; cc++) {
+          uint32_t r[32]; tc_ld32(taddr + cc * 32, r); tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; i++) {
+            float h = rnd<T>(__uint_as_float(r[i]));
+            if (bias) h = rnd<T>(h + to_f<T>(bias[wcol0 + cc * 32 + i]));
+            float d = h - mean; qs += d * d;
+          }
+        }
+        rstd = rsqrtf(qs / (float)BN + a.ep.eps);
+      }
+      for (int cc = 0; cc < BN / 32; cc++) {
+        uint32_t r[32]; tc_ld32(taddr + cc * 32, r); tc_wait_ld();
+        if (orow < 0) continue;
+        const int col = cot * BN + cc * 32;
+        float h[32];
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+          float v = rnd<T>(__uint_as_float(r[i]));
+          if (bias) v = rnd<T>(v + to_f<T>(bias[wcol0 + cc * 32 + i]));
+          h[i] = v;
+        }
+        if (a.ep.ln) {
+#pragma unroll
+          for (int i = 0; i < 32; i++) {
+            float v = rstd * (h[i] - mean);
+            if (a.ep.gamma) v = a.ep.gamma[col + i] * v;
+            if (a.ep.beta) v = v + a.ep.beta[col + i];
+            h[i] = rnd<T>(v);
+          }
+        }
+        if (a.ep.act) {
+#pragma unroll
+          for (int i = 0; i < 32; i++) h[i] = rnd<T>(act_apply(h[i], a.ep.act));
+        }
+        if (res) {
+          const uint4* rp = (const uint4*)(res + (i64)orow * a.Co + col);
+#pragma unroll
+          for (int g = 0; g < 4; g++) {
+            uint4 rv = __ldg(rp + g); const uint32_t* w32 = (const uint32_t*)&rv;
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+              float2 f = unpack2<T>(w32[e]);
+              h[g * 8 + e * 2] = rnd<T>(h[g * 8 + e * 2] + f.x); h[g * 8 + e * 2 + 1] = rnd<T>(h[g * 8 + e * 2 + 1] + f.y);
+            }
+          }
+        }
+        if (skx) {
+          const T* sx = skx + (i64)sp * a.ep.skip_cin + ss * (a.ep.skip_cin / 8);
+#pragma unroll
+          for (int i = 0; i < 32; i++) h[i] = rnd<T>(h[i] + to_f<T>(sx[(col + i) / a.ep.skip_rep]));
+        }
+        uint4* yp = (uint4*)(y + (i64)orow * a.Co + col);
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+          uint4 o;
+          o.x = pack2<T>(h[g * 8 + 0], h[g * 8 + 1]); o.y = pack2<T>(h[g * 8 + 2], h[g * 8 + 3]);
+          o.z = pack2<T>(h[g * 8 + 4], h[g * 8 + 5]); o.w = pack2<T>(h[g * 8 + 6], h[g * 8 + 7]);
+          yp[g] = o;
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar_acce + 8 * buf);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {        // a wait gave up: let copies still in flight land before the smem and TMEM are released
+    long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) {}
+    __syncthreads();
+  }
+  if (warp == WARP_MMA) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr; cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+    return (EncodeTiledFn)p;
+  }();
+  return fn;
+}
+
+template <int BN, class T>
+int launch_bn(t2sc_ctx* ctx, const CUtensorMap& tm, const ConvArgs& args, i64 max_items) {
+  constexpr int smem = num_stages(BN) * stage_bytes(BN) + aux_bytes() + 1024;
+  static_assert(smem <= SMEM_BUDGET, "shared memory budget");
+  static bool attr_set[16] = {};
+  if (!attr_set[ctx->device & 15]) {
+    T2_CUDA(ctx, cudaFuncSetAttribute(k_conv_umma<BN, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attr_set[ctx->device & 15] = true;
+  }
+  int grid = (int)(max_items < ctx->num_sms ? max_items : ctx->num_sms);
+  k_conv_umma<BN, T><<<grid, NTHREADS, smem, ctx->stream>>>(tm, args);
+  T2_LAUNCHED(ctx);
+  return T2SC_OK;
+}
+
+template <class T>
+int launch_t(t2sc_ctx* ctx, int BN, const CUtensorMap& tm, const ConvArgs& args, i64 max_items) {
+  switch (BN) {
+    case 256: return launch_bn<256, T>(ctx, tm, args, max_items);
+    case 128: return launch_bn<128, T>(ctx, tm, args, max_items);
+    case 64: return launch_bn<64, T>(ctx, tm, args, max_items);
+    default: return launch_bn<32, T>(ctx, tm, args, max_items);
+  }
+}
+
+int pick_bn(int Co) {
+  for (int bn : {256, 128, 64, 32}) if (Co % bn == 0) return bn;
+  return 0;
+}
+
+}  // namespace
+
+bool conv_umma_supported(int dtype, int Ci, int Co, const EpiDev& ep) {
+  (void)ep;
+  return (dtype == T2SC_F16 || dtype == T2SC_BF16) && Ci % KCH == 0 && Co % 32 == 0;
+}
+
+int conv_umma_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const void* w, i64 w_rows, const EpiDev& ep, void* y,
+                     int dtype, i64 n_in, int Ci, int Co) {
+  (void)n_in;
+  T2_CUDA(ctx, cudaSetDevice(ctx->device));
+  const int BN = pick_bn(Co);
+  T2_REQ(ctx, BN > 0, "Co=%d", Co);
+  T2_REQ(ctx, !ep.ln || Co == BN, "fused LayerNorm needs the whole row in one tile (Co=%d)", Co);
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return t2sc_fail(ctx, T2SC_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  // weights [w_rows, 27, Ci] as a 3-D tensor (innermost first): Ci, 27, w_rows; box = 64 channels x 1 tap x BN rows
+  CUtensorMap tm;
+  cuuint64_t dims[3] = {(cuuint64_t)Ci, 27, (cuuint64_t)w_rows};
+  cuuint64_t strides[2] = {(cuuint64_t)Ci * 2, (cuuint64_t)Ci * 2 * 27};
+  cuuint32_t box[3] = {(cuuint32_t)KCH, 1, (cuuint32_t)BN};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult cr = enc(&tm, dtype == T2SC_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(w),
+                    dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (cr != CUDA_SUCCESS) return t2sc_fail(ctx, T2SC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for weights [%lld,27,%d]", (int)cr, (long long)w_rows, Ci);
+  ConvArgs args;
+  args.x = x; args.y = y; args.nbr = plan->nbr; args.order = plan->order; args.src = plan->src;
+  args.tiles = plan->tiles; args.ntiles = plan->ntiles; args.status = ctx->status;
+  args.Ci = Ci; args.Co = Co; args.n_cot = Co / BN; args.is_bf16 = dtype == T2SC_BF16; args.ep = ep;
+  i64 max_items = plan->max_tiles * args.n_cot;
+  if (dtype == T2SC_BF16) return launch_t<__nv_bfloat16>(ctx, BN, tm, args, max_items);
+  return launch_t<__half>(ctx, BN, tm, args, max_items);
+}

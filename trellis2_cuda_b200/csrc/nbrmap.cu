@@ -1,0 +1,278 @@
+// Integer half of the path: voxel hash table, 27-tap neighbour maps, the reference's row order and
+// per-block tap lists, 2x subdivision maps, row gather and the up-block skip add.
+//
+// Results are defined by the reference (src/spconv.cu:13-75, src/sdec.cu:21-57 of trellis2-cuda) and are
+// bit-exact with it; the layout of the work is not.  The table packs key and value into one 16-byte
+// slot so a probe is a single 128-bit load, the neighbour kernel maps one thread to one (row, tap) entry
+// so the 108-byte rows of nbr are written fully coalesced, and nothing is built on the host.
+#include "common.cuh"
+#include <cub/cub.cuh>
+
+namespace {
+
+struct __align__(16) Slot { unsigned long long key; uint32_t val; uint32_t pad; };
+static constexpr unsigned long long KEY_EMPTY = ~0ull;
+
+__device__ __forceinline__ uint32_t mix32(unsigned long long k) {   // src/spconv.cu:13
+  k ^= k >> 33; k *= 0xff51afd7ed558ccdull; k ^= k >> 33; return (uint32_t)k;
+}
+__device__ __forceinline__ unsigned long long pack_key(int b, int x, int y, int z, int W, int H, int D) {  // src/spconv.cu:16
+  return (((unsigned long long)b * W + x) * H + y) * D + z;
+}
+
+__global__ void k_hash_insert(const int4* __restrict__ coords, int n, int W, int H, int D, Slot* table, uint32_t mask) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int4 q = coords[i];
+  unsigned long long k = pack_key(q.x, q.y, q.z, q.w, W, H, D);
+  // at most `mask + 1` probes: the table holds >= 2n slots, so this bound is never reached on valid input
+  for (uint32_t s = mix32(k) & mask, it = 0; it <= mask; s = (s + 1) & mask, ++it) {
+    unsigned long long prev = atomicCAS(&table[s].key, KEY_EMPTY, k);
+    if (prev == KEY_EMPTY || prev == k) { atomicMin(&table[s].val, (uint32_t)i); return; }  // duplicates: lowest row wins
+  }
+}
+
+constexpr int NB_ROWS = 32;                 // rows per CTA of the neighbour kernel
+constexpr int NB_THREADS = 288;             // 32 rows * 27 taps = 864 entries = 3 per thread
+__global__ void __launch_bounds__(NB_THREADS) k_neighbors(const int4* __restrict__ coords, int n, int W, int H, int D,
+                                                          const Slot* __restrict__ table, uint32_t mask,
+                                                          uint32_t* __restrict__ nbr, int* __restrict__ gray, int* __restrict__ bin) {
+  __shared__ uint32_t s_mask[NB_ROWS];
+  i64 row0 = (i64)blockIdx.x * NB_ROWS;
+  if (threadIdx.x < NB_ROWS) s_mask[threadIdx.x] = 0;
+  __syncthreads();
+  int rows = (int)min((i64)NB_ROWS, (i64)n - row0);
+#pragma unroll
+  for (int e = threadIdx.x; e < NB_ROWS * 27; e += NB_THREADS) {
+    int lr = e / 27, v = e - lr * 27;
+    if (lr >= rows) break;
+    int4 q = coords[row0 + lr];
+    int x = q.y + v / 9 - 1, y = q.z + (v / 3) % 3 - 1, z = q.w + v % 3 - 1;   // src/spconv.cu:27
+    uint32_t r = NBR_EMPTY;
+    if (x >= 0 && x < W && y >= 0 && y < H && z >= 0 && z < D) {
+      unsigned long long k = pack_key(q.x, x, y, z, W, H, D);
+      for (uint32_t s = mix32(k) & mask, it = 0; it <= mask; s = (s + 1) & mask, ++it) {
+        uint4 raw = __ldg(reinterpret_cast<const uint4*>(table + s));
+        unsigned long long sk = ((unsigned long long)raw.y << 32) | raw.x;
+        if (sk == KEY_EMPTY) break;
+        if (sk == k) { r = raw.z; break; }
+      }
+    }
+    nbr[(row0 + lr) * 27 + v] = r;
+    if (r != NBR_EMPTY) atomicOr(&s_mask[lr], 1u << v);
+  }
+  __syncthreads();
+  if (threadIdx.x < rows) {
+    uint32_t g = s_mask[threadIdx.x], b = g;
+#pragma unroll
+    for (int v = 1; v < 27; v++) b ^= g >> v;       // gray -> binary, src/spconv.cu:34
+    gray[row0 + threadIdx.x] = (int)g;
+    if (bin) bin[row0 + threadIdx.x] = (int)b;
+  }
+}
+
+__global__ void k_iota(int* p, int n) { int i = blockIdx.x * blockDim.x + threadIdx.x; if (i < n) p[i] = i; }
+
+// ---- valid(B1): one warp per block of B1 sorted rows
+__global__ void k_block_or(const int* __restrict__ gray, const int* __restrict__ sorted, int n, int B1, int nb,
+                           int* __restrict__ code, int* __restrict__ cnt) {
+  int b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (b >= nb) return;
+  int o = 0;
+  i64 lo = (i64)b * B1, hi = min((i64)n, lo + B1);
+  for (i64 i = lo + lane; i < hi; i += 32) o |= gray[sorted[i]];
+  o = __reduce_or_sync(0xffffffffu, (unsigned)o);
+  if (lane == 0) { code[b] = o; cnt[b] = __popc(o); }
+}
+__global__ void k_block_list(const int* __restrict__ code, const int* __restrict__ seg, int nb, int* __restrict__ list) {
+  int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= nb) return;
+  int c = code[b], s = seg[b];
+  while (c) { list[s++] = __ffs(c) - 1; c &= c - 1; }
+}
+
+// ---- 2x subdivision
+template <class T> __device__ __forceinline__ bool sub_keep(const T* sub, i64 e);
+template <> __device__ __forceinline__ bool sub_keep<__half>(const __half* s, i64 e) { return __half2float(s[e]) > 0.f; }
+template <> __device__ __forceinline__ bool sub_keep<__nv_bfloat16>(const __nv_bfloat16* s, i64 e) { return __bfloat162float(s[e]) > 0.f; }
+template <> __device__ __forceinline__ bool sub_keep<uint8_t>(const uint8_t* s, i64 e) { return s[e] != 0; }
+
+template <class T> __global__ void k_c2s_count(const T* __restrict__ sub, int n, int* __restrict__ cnt) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int c = 0;
+#pragma unroll
+  for (int s = 0; s < 8; s++) c += sub_keep<T>(sub, (i64)i * 8 + s);
+  cnt[i] = c;
+}
+template <class T> __global__ void k_c2s_emit(const T* __restrict__ sub, const int4* __restrict__ co, const int* __restrict__ off,
+                                              int n, int4* __restrict__ nco, int* __restrict__ src) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int r = off[i]; int4 q = co[i];
+#pragma unroll
+  for (int s = 0; s < 8; s++)
+    if (sub_keep<T>(sub, (i64)i * 8 + s)) {
+      nco[r] = make_int4(q.x, q.y * 2 + (s & 1), q.z * 2 + (s >> 1 & 1), q.w * 2 + (s >> 2 & 1));
+      src[r++] = i * 8 + s;
+    }
+}
+
+// ---- row gather / skip add, 16 bytes per thread
+__global__ void k_gather_rows16(const uint4* __restrict__ x, const int* __restrict__ src, i64 m, int vec_per_row, uint4* __restrict__ y) {
+  i64 i = blockIdx.x * (i64)blockDim.x + threadIdx.x;
+  if (i >= m * vec_per_row) return;
+  i64 r = i / vec_per_row; int c = (int)(i - r * vec_per_row);
+  y[i] = __ldg(x + (i64)src[r] * vec_per_row + c);
+}
+template <class T> __global__ void k_add_skip(T* __restrict__ h, const T* __restrict__ x, const int* __restrict__ src, i64 m,
+                                              int Co, int Cin, int rep) {
+  i64 i = blockIdx.x * (i64)blockDim.x + threadIdx.x;
+  if (i >= m * Co) return;
+  i64 r = i / Co; int c = (int)(i - r * Co), p = src[r] >> 3, s = src[r] & 7, Cs = Cin / 8;
+  h[i] = from_f<T>(to_f<T>(h[i]) + to_f<T>(x[(i64)p * Cin + s * Cs + c / rep]));
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------ entry points
+extern "C" int t2sc_build_neighbors(t2sc_ctx* ctx, const int32_t* coords, int64_t n, int W, int H, int D,
+                                    uint32_t* nbr, int32_t* gray, int32_t* sorted) {
+  T2_REQ(ctx, ctx != nullptr, "null context");
+  T2_REQ(ctx, n >= 0 && n < (1ll << 30), "n=%lld", (long long)n);
+  if (n == 0) return T2SC_OK;
+  T2_REQ(ctx, coords && nbr && gray, "null tensor");
+  T2_REQ(ctx, (uintptr_t)coords % 16 == 0, "coords must be 16-byte aligned");
+  T2_REQ(ctx, W > 0 && H > 0 && D > 0, "grid extent %d %d %d", W, H, D);
+  T2_CUDA(ctx, cudaSetDevice(ctx->device));
+  uint32_t cap = 1; while (cap < 2u * (uint32_t)n) cap <<= 1;            // src/spconv.cu:40
+  Slot* table = nullptr; int* bin = nullptr;
+  T2_CUDA(ctx, t2_alloc(ctx, &table, cap));
+  T2_CUDA(ctx, cudaMemsetAsync(table, 0xff, (size_t)cap * sizeof(Slot), ctx->stream));
+  k_hash_insert<<<cdiv_i(n, 256), 256, 0, ctx->stream>>>((const int4*)coords, (int)n, W, H, D, table, cap - 1);
+  T2_LAUNCHED(ctx);
+  if (sorted) T2_CUDA(ctx, t2_alloc(ctx, &bin, (size_t)n));
+  k_neighbors<<<cdiv_i(n, NB_ROWS), NB_THREADS, 0, ctx->stream>>>((const int4*)coords, (int)n, W, H, D, table, cap - 1, nbr, gray, bin);
+  T2_LAUNCHED(ctx);
+  t2_free(ctx, table);
+  if (sorted) {
+    int *bs = nullptr, *iota = nullptr; void* tmp = nullptr; size_t tb = 0;
+    T2_CUDA(ctx, t2_alloc(ctx, &bs, (size_t)n));
+    T2_CUDA(ctx, t2_alloc(ctx, &iota, (size_t)n));
+    k_iota<<<cdiv_i(n, 256), 256, 0, ctx->stream>>>(iota, (int)n);
+    T2_LAUNCHED(ctx);
+    // the key has 27 significant bits; radix sort is stable, so ties keep ascending row order
+    T2_CUDA(ctx, cub::DeviceRadixSort::SortPairs(nullptr, tb, bin, bs, iota, sorted, (int)n, 0, 27, ctx->stream));
+    T2_CUDA(ctx, t2_alloc(ctx, (char**)&tmp, tb));
+    T2_CUDA(ctx, cub::DeviceRadixSort::SortPairs(tmp, tb, bin, bs, iota, sorted, (int)n, 0, 27, ctx->stream));
+    t2_free(ctx, tmp); t2_free(ctx, bs); t2_free(ctx, iota); t2_free(ctx, bin);
+  }
+  return T2SC_OK;
+}
+
+extern "C" int t2sc_valid_taps(t2sc_ctx* ctx, const int32_t* gray, const int32_t* sorted, int64_t n, int B1,
+                               int32_t* seg, int32_t* list, int64_t* total_host) {
+  T2_REQ(ctx, ctx != nullptr, "null context");
+  T2_REQ(ctx, n >= 0 && B1 > 0, "n=%lld B1=%d", (long long)n, B1);
+  if (total_host) *total_host = 0;
+  if (n == 0) return T2SC_OK;
+  T2_REQ(ctx, gray && sorted && seg && list, "null tensor");
+  T2_CUDA(ctx, cudaSetDevice(ctx->device));
+  int nb = cdiv_i(n, B1);
+  int* code = nullptr; void* tmp = nullptr; size_t tb = 0;
+  T2_CUDA(ctx, t2_alloc(ctx, &code, (size_t)nb));
+  T2_CUDA(ctx, cudaMemsetAsync(seg, 0, sizeof(int), ctx->stream));
+  k_block_or<<<cdiv_i((i64)nb * 32, 256), 256, 0, ctx->stream>>>(gray, sorted, (int)n, B1, nb, code, seg + 1);
+  T2_LAUNCHED(ctx);
+  T2_CUDA(ctx, cub::DeviceScan::InclusiveSum(nullptr, tb, seg + 1, seg + 1, nb, ctx->stream));
+  T2_CUDA(ctx, t2_alloc(ctx, (char**)&tmp, tb));
+  T2_CUDA(ctx, cub::DeviceScan::InclusiveSum(tmp, tb, seg + 1, seg + 1, nb, ctx->stream));
+  k_block_list<<<cdiv_i(nb, 256), 256, 0, ctx->stream>>>(code, seg, nb, list);
+  T2_LAUNCHED(ctx);
+  t2_free(ctx, tmp); t2_free(ctx, code);
+  if (total_host) {
+    int tot = 0;
+    T2_CUDA(ctx, cudaMemcpyAsync(&tot, seg + nb, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    T2_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    *total_host = tot;
+  }
+  return T2SC_OK;
+}
+
+extern "C" int t2sc_subdivide_count(t2sc_ctx* ctx, const void* sub, int sub_dtype, int64_t n, int32_t* off, int64_t* m_host) {
+  T2_REQ(ctx, ctx != nullptr, "null context");
+  T2_REQ(ctx, n >= 0 && n < (1ll << 28), "n=%lld", (long long)n);
+  T2_REQ(ctx, sub_dtype == T2SC_F16 || sub_dtype == T2SC_BF16 || sub_dtype == T2SC_U8, "sub dtype %d", sub_dtype);
+  if (m_host) *m_host = 0;
+  T2_REQ(ctx, off != nullptr, "null off");
+  T2_CUDA(ctx, cudaSetDevice(ctx->device));
+  T2_CUDA(ctx, cudaMemsetAsync(off, 0, sizeof(int), ctx->stream));
+  if (n == 0) return T2SC_OK;
+  T2_REQ(ctx, sub != nullptr, "null sub");
+  int* cnt = nullptr; void* tmp = nullptr; size_t tb = 0;
+  T2_CUDA(ctx, t2_alloc(ctx, &cnt, (size_t)n));
+  int g = cdiv_i(n, 256);
+  if (sub_dtype == T2SC_F16) k_c2s_count<__half><<<g, 256, 0, ctx->stream>>>((const __half*)sub, (int)n, cnt);
+  else if (sub_dtype == T2SC_BF16) k_c2s_count<__nv_bfloat16><<<g, 256, 0, ctx->stream>>>((const __nv_bfloat16*)sub, (int)n, cnt);
+  else k_c2s_count<uint8_t><<<g, 256, 0, ctx->stream>>>((const uint8_t*)sub, (int)n, cnt);
+  T2_LAUNCHED(ctx);
+  T2_CUDA(ctx, cub::DeviceScan::InclusiveSum(nullptr, tb, cnt, off + 1, (int)n, ctx->stream));
+  T2_CUDA(ctx, t2_alloc(ctx, (char**)&tmp, tb));
+  T2_CUDA(ctx, cub::DeviceScan::InclusiveSum(tmp, tb, cnt, off + 1, (int)n, ctx->stream));
+  t2_free(ctx, tmp); t2_free(ctx, cnt);
+  if (m_host) {
+    int m = 0;
+    T2_CUDA(ctx, cudaMemcpyAsync(&m, off + n, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    T2_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    *m_host = m;
+  }
+  return T2SC_OK;
+}
+
+extern "C" int t2sc_subdivide_emit(t2sc_ctx* ctx, const void* sub, int sub_dtype, const int32_t* coords, const int32_t* off,
+                                   int64_t n, int32_t* child_coords, int32_t* src) {
+  T2_REQ(ctx, ctx != nullptr, "null context");
+  T2_REQ(ctx, n >= 0 && n < (1ll << 28), "n=%lld", (long long)n);
+  T2_REQ(ctx, sub_dtype == T2SC_F16 || sub_dtype == T2SC_BF16 || sub_dtype == T2SC_U8, "sub dtype %d", sub_dtype);
+  if (n == 0) return T2SC_OK;
+  T2_REQ(ctx, sub && coords && off && child_coords && src, "null tensor");
+  T2_REQ(ctx, (uintptr_t)coords % 16 == 0 && (uintptr_t)child_coords % 16 == 0, "coords must be 16-byte aligned");
+  T2_CUDA(ctx, cudaSetDevice(ctx->device));
+  int g = cdiv_i(n, 256);
+  if (sub_dtype == T2SC_F16)
+    k_c2s_emit<__half><<<g, 256, 0, ctx->stream>>>((const __half*)sub, (const int4*)coords, off, (int)n, (int4*)child_coords, src);
+  else if (sub_dtype == T2SC_BF16)
+    k_c2s_emit<__nv_bfloat16><<<g, 256, 0, ctx->stream>>>((const __nv_bfloat16*)sub, (const int4*)coords, off, (int)n, (int4*)child_coords, src);
+  else
+    k_c2s_emit<uint8_t><<<g, 256, 0, ctx->stream>>>((const uint8_t*)sub, (const int4*)coords, off, (int)n, (int4*)child_coords, src);
+  T2_LAUNCHED(ctx);
+  return T2SC_OK;
+}
+
+extern "C" int t2sc_gather_rows(t2sc_ctx* ctx, const void* x, const int32_t* src, int64_t m, int C, int dtype, void* y) {
+  T2_REQ(ctx, ctx != nullptr, "null context");
+  size_t row_bytes = (size_t)C * dtype_size(dtype);
+  T2_REQ(ctx, m >= 0 && C > 0 && row_bytes % 16 == 0, "m=%lld C=%d: rows must be a multiple of 16 bytes", (long long)m, C);
+  if (m == 0) return T2SC_OK;
+  T2_REQ(ctx, x && src && y && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0, "null or unaligned tensor");
+  T2_CUDA(ctx, cudaSetDevice(ctx->device));
+  int vpr = (int)(row_bytes / 16);
+  k_gather_rows16<<<cdiv_i(m * vpr, 256), 256, 0, ctx->stream>>>((const uint4*)x, src, m, vpr, (uint4*)y);
+  T2_LAUNCHED(ctx);
+  return T2SC_OK;
+}
+
+extern "C" int t2sc_add_skip(t2sc_ctx* ctx, void* h, const void* x, const int32_t* src, int64_t m, int Co, int Cin, int rep, int dtype) {
+  T2_REQ(ctx, ctx != nullptr, "null context");
+  T2_REQ(ctx, m >= 0 && Co > 0 && Cin % 8 == 0 && rep > 0 && Co == (Cin / 8) * rep, "m=%lld Co=%d Cin=%d rep=%d", (long long)m, Co, Cin, rep);
+  if (m == 0) return T2SC_OK;
+  T2_REQ(ctx, h && x && src, "null tensor");
+  T2_CUDA(ctx, cudaSetDevice(ctx->device));
+  int g = cdiv_i(m * Co, 256);
+  if (dtype == T2SC_F16) k_add_skip<__half><<<g, 256, 0, ctx->stream>>>((__half*)h, (const __half*)x, src, m, Co, Cin, rep);
+  else if (dtype == T2SC_BF16) k_add_skip<__nv_bfloat16><<<g, 256, 0, ctx->stream>>>((__nv_bfloat16*)h, (const __nv_bfloat16*)x, src, m, Co, Cin, rep);
+  else if (dtype == T2SC_F32) k_add_skip<float><<<g, 256, 0, ctx->stream>>>((float*)h, (const float*)x, src, m, Co, Cin, rep);
+  else return t2sc_fail(ctx, T2SC_ERR_ARG, "dtype %d", dtype);
+  T2_LAUNCHED(ctx);
+  return T2SC_OK;
+}

@@ -1,0 +1,155 @@
+// Execution plan: which output rows share a 128-row tile, and which taps each tile has to visit.
+//
+// The reference schedules by a global stable sort of the gray->binary mask key and per-block tap lists
+// (src/spconv.cu:34,47-75 of trellis2-cuda).  Here the sort key is (weight group, run of block_rows caller
+// rows, mask key): rows with similar masks still become adjacent, which keeps the union mask of a tile
+// close to its rows' own masks, but only inside a run of caller rows, so the gathers of one tile stay
+// inside a region that fits the L2.  Weight groups are the 8 child slots of a 2x-subdivision conv.
+// Everything is built on the device; no host round trip is needed to launch a conv from a plan.
+#include "common.cuh"
+#include <cub/cub.cuh>
+
+namespace {
+
+constexpr int TILE = 128;
+
+__device__ __forceinline__ uint32_t gray_to_bin(uint32_t g) {
+  uint32_t b = g;
+#pragma unroll
+  for (int v = 1; v < 27; v++) b ^= g >> v;
+  return b;
+}
+
+// key = group | block (block_bits wide) | mask key (27 bits), most significant first
+__global__ void k_plan_keys(const int* __restrict__ gray, const int* __restrict__ src, i64 m, i64 block_rows, int block_bits,
+                            unsigned long long* __restrict__ keys, int* __restrict__ iota, int* __restrict__ group_cnt) {
+  i64 i = blockIdx.x * (i64)blockDim.x + threadIdx.x;
+  if (i >= m) return;
+  int grp = 0; i64 nrow = i;
+  if (src) { int s = src[i]; grp = s & 7; nrow = s >> 3; }
+  unsigned long long blk = (unsigned long long)(i / block_rows);
+  keys[i] = ((unsigned long long)grp << (27 + block_bits)) | (blk << 27) | gray_to_bin((uint32_t)gray[nrow]);
+  iota[i] = (int)i;
+  if (src) atomicAdd(&group_cnt[grp], 1);
+}
+
+// one thread: tile offsets of the (up to 8) groups
+__global__ void k_plan_groups(const int* __restrict__ group_cnt, int ngroups, i64 m, int* __restrict__ gmeta, int* __restrict__ ntiles) {
+  // gmeta[g] = first row of group g, gmeta[16+g] = first tile of group g
+  int row = 0, tile = 0;
+  for (int g = 0; g < ngroups; g++) {
+    int c = ngroups == 1 ? (int)m : group_cnt[g];
+    gmeta[g] = row; gmeta[16 + g] = tile;
+    row += c; tile += (c + TILE - 1) / TILE;
+  }
+  gmeta[ngroups] = row; gmeta[16 + ngroups] = tile;
+  *ntiles = tile;
+}
+
+// one warp per tile: extent, weight base, OR of the row masks; also the plan's tap statistics
+__global__ void k_plan_tiles(const int* __restrict__ gray, const int* __restrict__ src, const int* __restrict__ order,
+                             const int* __restrict__ gmeta, int ngroups, int co_per_group, const int* __restrict__ ntiles,
+                             PlanTile* __restrict__ tiles, unsigned long long* __restrict__ stats) {
+  int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (t >= *ntiles) return;
+  int g = 0;
+  while (g + 1 < ngroups && t >= gmeta[16 + g + 1]) g++;
+  int start = gmeta[g] + (t - gmeta[16 + g]) * TILE;
+  int rows = min(TILE, gmeta[g + 1] - start);
+  uint32_t o = 0; int act = 0;
+  for (int j = lane; j < rows; j += 32) {
+    int r = order[start + j];
+    int nrow = src ? (src[r] >> 3) : r;
+    uint32_t gm = (uint32_t)gray[nrow];
+    o |= gm; act += __popc(gm);
+  }
+  o = __reduce_or_sync(0xffffffffu, o);
+  act = __reduce_add_sync(0xffffffffu, act);
+  if (lane == 0) {
+    tiles[t] = PlanTile{start, rows, g, o};      // wbase holds the group; the conv multiplies by Co
+    atomicAdd(&stats[0], (unsigned long long)rows * __popc(o));
+    atomicAdd(&stats[1], (unsigned long long)act);
+  }
+  (void)co_per_group;
+}
+
+}  // namespace
+
+extern "C" int t2sc_plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_t* gray, int64_t n_rows,
+                                const int32_t* src, int64_t m, int64_t block_rows, t2sc_plan** out) {
+  T2_REQ(ctx, ctx && out, "null context or out");
+  *out = nullptr;
+  T2_REQ(ctx, n_rows >= 0 && m >= 0 && m < (1ll << 30) && n_rows < (1ll << 30), "n_rows=%lld m=%lld", (long long)n_rows, (long long)m);
+  if (!src) T2_REQ(ctx, m == n_rows, "a submanifold plan has one output row per neighbour row (m=%lld n_rows=%lld)", (long long)m, (long long)n_rows);
+  T2_REQ(ctx, m == 0 || (nbr && gray), "null tensor");
+  T2_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (block_rows <= 0) block_rows = 1 << 16;
+  T2_REQ(ctx, (m + block_rows - 1) / block_rows < (1ll << 23), "block_rows=%lld too small for m=%lld", (long long)block_rows, (long long)m);
+  t2sc_plan* p = new t2sc_plan();
+  p->n_out = m; p->n_rows = n_rows; p->nbr = nbr; p->src = src;
+  int ngroups = src ? 8 : 1;
+  p->max_tiles = cdiv_i(m, TILE) + (src ? 8 : 0);
+  unsigned long long *keys = nullptr, *keys2 = nullptr; int *iota = nullptr, *gcnt = nullptr, *gmeta = nullptr; void* tmp = nullptr;
+  auto fail = [&](cudaError_t e) {
+    t2_free(ctx, keys); t2_free(ctx, keys2); t2_free(ctx, iota); t2_free(ctx, gcnt); t2_free(ctx, gmeta); t2_free(ctx, tmp);
+    t2sc_plan_destroy(ctx, p);
+    return t2sc_fail(ctx, T2SC_ERR_CUDA, "t2sc_plan_create: %s", cudaGetErrorString(e));
+  };
+  cudaError_t e;
+#define PL(call) do { if ((e = (call)) != cudaSuccess) return fail(e); } while (0)
+  PL(t2_alloc(ctx, &p->order, (size_t)m));
+  PL(t2_alloc(ctx, &p->tiles, (size_t)p->max_tiles));
+  PL(t2_alloc(ctx, &p->ntiles, 1));
+  PL(t2_alloc(ctx, &p->stats, 2));
+  PL(cudaMemsetAsync(p->ntiles, 0, sizeof(int), ctx->stream));
+  PL(cudaMemsetAsync(p->stats, 0, 2 * sizeof(unsigned long long), ctx->stream));
+  if (m > 0) {
+    PL(t2_alloc(ctx, &keys, (size_t)m)); PL(t2_alloc(ctx, &keys2, (size_t)m)); PL(t2_alloc(ctx, &iota, (size_t)m));
+    PL(t2_alloc(ctx, &gcnt, 8)); PL(t2_alloc(ctx, &gmeta, 32));
+    PL(cudaMemsetAsync(gcnt, 0, 8 * sizeof(int), ctx->stream));
+    int block_bits = 0;
+    while (((m + block_rows - 1) / block_rows) > (1ll << block_bits)) block_bits++;
+    k_plan_keys<<<cdiv_i(m, 256), 256, 0, ctx->stream>>>(gray, src, m, block_rows, block_bits, keys, iota, gcnt);
+    ctx->launches++; PL(cudaGetLastError());
+    size_t tb = 0;
+    int end_bit = 27 + block_bits + (src ? 3 : 0);
+    PL(cub::DeviceRadixSort::SortPairs(nullptr, tb, keys, keys2, iota, p->order, (int)m, 0, end_bit, ctx->stream));
+    PL(t2_alloc(ctx, (char**)&tmp, tb));
+    PL(cub::DeviceRadixSort::SortPairs(tmp, tb, keys, keys2, iota, p->order, (int)m, 0, end_bit, ctx->stream));
+    k_plan_groups<<<1, 1, 0, ctx->stream>>>(gcnt, ngroups, m, gmeta, p->ntiles);
+    ctx->launches++; PL(cudaGetLastError());
+    k_plan_tiles<<<cdiv_i(p->max_tiles * 32, 256), 256, 0, ctx->stream>>>(gray, src, p->order, gmeta, ngroups, 0, p->ntiles, p->tiles, p->stats);
+    ctx->launches++; PL(cudaGetLastError());
+  }
+#undef PL
+  t2_free(ctx, keys); t2_free(ctx, keys2); t2_free(ctx, iota); t2_free(ctx, gcnt); t2_free(ctx, gmeta); t2_free(ctx, tmp);
+  *out = p;
+  return T2SC_OK;
+}
+
+extern "C" int t2sc_plan_destroy(t2sc_ctx* ctx, t2sc_plan* p) {
+  if (!p) return T2SC_OK;
+  T2_REQ(ctx, ctx != nullptr, "null context");
+  cudaSetDevice(ctx->device);
+  t2_free(ctx, p->order); t2_free(ctx, p->tiles); t2_free(ctx, p->ntiles); t2_free(ctx, p->stats);
+  delete p;
+  return T2SC_OK;
+}
+
+extern "C" int t2sc_plan_stats(t2sc_ctx* ctx, t2sc_plan* p, int64_t* tiles, int64_t* computed_taps, int64_t* active_taps) {
+  T2_REQ(ctx, ctx && p, "null context or plan");
+  int nt = 0; unsigned long long st[2] = {0, 0};
+  T2_CUDA(ctx, cudaMemcpyAsync(&nt, p->ntiles, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+  T2_CUDA(ctx, cudaMemcpyAsync(st, p->stats, sizeof(st), cudaMemcpyDeviceToHost, ctx->stream));
+  T2_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (tiles) *tiles = nt;
+  if (computed_taps) *computed_taps = (int64_t)st[0];
+  if (active_taps) *active_taps = (int64_t)st[1];
+  return T2SC_OK;
+}
+
+extern "C" int t2sc_plan_order(t2sc_ctx* ctx, t2sc_plan* p, int32_t* order_out) {
+  T2_REQ(ctx, ctx && p && (order_out || p->n_out == 0), "null argument");
+  if (p->n_out) T2_CUDA(ctx, cudaMemcpyAsync(order_out, p->order, (size_t)p->n_out * sizeof(int), cudaMemcpyDeviceToDevice, ctx->stream));
+  return T2SC_OK;
+}
