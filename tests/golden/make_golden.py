@@ -63,7 +63,7 @@ def main(out):
     G.update(c2s_coords=c, c2s_sub=sub, c2s_child=cc, c2s_src=src)
     # --- convs (fp16)
     c = random_coords(rng, 640, 9, 1)
-    for tag, Ci, Co, use_b in (("f0", 64, 64, True), ("f1", 32, 96, False), ("f2", 128, 256, True)):
+    for tag, Ci, Co, use_b in (("f0", 64, 64, True), ("f1", 64, 96, False), ("f2", 128, 256, True)):
         x = rng.standard_normal((c.shape[0], Ci)).astype(np.float16)
         w = weight(Co, Ci, 7)
         b = (0.1 * rng.standard_normal(Co)).astype(np.float16) if use_b else None
@@ -83,7 +83,7 @@ def main(out):
     G.update(b0_coords=c, b0_x=x, b0_w_sha=sha(w), b0_b=b, b0_g=g, b0_be=be, b0_y_ln_gelu_res=y0, b0_y_ln_silu=y1)
     # --- tail of the up block: conv1 -> c2s -> gather -> LN -> SiLU -> conv2 -> skip
     c = random_coords(rng, 400, 8, 1)
-    Ci, Cc = 64, 32
+    Ci, Cc = 128, 64
     x = rng.standard_normal((c.shape[0], Ci)).astype(np.float16)
     sub = rng.standard_normal((c.shape[0], 8)).astype(np.float16)
     w1 = weight(8 * Cc, Ci, 9)

@@ -31,13 +31,22 @@ def host(t):
     return t.float().cpu().numpy() if t.is_floating_point() else t.cpu().numpy()
 
 
-def check_feats(got, want, what=""):
+ULP = {"f16": 2.0 ** -10, "bf16": 2.0 ** -7, "f32": 2.0 ** -23}
+
+
+def check_feats(got, want, what="", dt=None):
+    """max-abs <= 2e-2 and mean-rel <= 2e-3.  With `dt` given (outputs that went through LayerNorm or an
+    activation, whose magnitude is not bounded near 1) one rounding step of the storage dtype is also
+    accepted where it exceeds 2e-2: a bf16 value in [4, 8) cannot differ by less than 3.1e-2."""
     got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
     assert got.shape == want.shape, what
     assert np.isfinite(got).all(), what
-    mx = np.abs(got - want).max()
-    mr = np.abs(got - want).sum() / max(np.abs(want).sum(), 1e-30)
-    assert mx <= MAX_ABS and mr <= MEAN_REL, f"{what}: max-abs {mx:.3e} mean-rel {mr:.3e}"
+    err = np.abs(got - want)
+    allow = np.full_like(err, MAX_ABS)
+    if dt is not None:
+        allow = np.maximum(allow, ULP[dt] * 2.0 ** np.floor(np.log2(np.maximum(np.abs(want), 1e-30))))
+    mr = err.sum() / max(np.abs(want).sum(), 1e-30)
+    assert (err <= allow).all() and mr <= MEAN_REL, f"{what}: max-abs {err.max():.3e} mean-rel {mr:.3e}"
 
 
 def random_coords(rng, n, res, batches=1):
@@ -53,7 +62,7 @@ def rounded(a, dt):
 
 
 # ------------------------------------------------------------------------------------------ integer maps
-@pytest.mark.parametrize("n,res,batches,ext", [(1, 4, 1, 4), (37, 4, 2, 4), (700, 10, 2, 10), (5000, 24, 1, 4096), (33, 3, 1, 3)])
+@pytest.mark.parametrize("n,res,batches,ext", [(1, 4, 1, 4), (37, 4, 2, 4), (700, 10, 2, 10), (5000, 24, 1, 4096), (27, 3, 1, 3)])
 def test_neighbors_bit_exact(sp, n, res, batches, ext):
     rng = np.random.default_rng(n)
     c = random_coords(rng, n, res, batches)
@@ -169,7 +178,7 @@ def test_fused_epilogues(sp, variant, dt):
         want = oracle.conv_block(x, w, b, nbr, dt, ln=ln, act_kind=act, residual=x if res else None)
         lnd = None if ln is None else (None if ln[0] is None else dev(ln[0]), None if ln[1] is None else dev(ln[1]), ln[2])
         y = sp.subm_conv(xd, wd, bd, cache, ln=lnd, act=act, residual=xd if res else None, variant=variant)
-        check_feats(host(y), want, f"{variant} {dt} ln={ln is not None} act={act} res={res}")
+        check_feats(host(y), want, f"{variant} {dt} ln={ln is not None} act={act} res={res}", dt)
     cache.ctx.device_status()
 
 
@@ -180,14 +189,14 @@ def test_fused_layernorm_wide_falls_back_to_row_pass(sp):
     want = oracle.conv_block(x, w, b, nbr, "bf16", ln=(None, None, 1e-6), act_kind="silu")
     y = sp.subm_conv(dev(x, torch.bfloat16), dev(w, torch.bfloat16), dev(b, torch.bfloat16), sp.build_neighbors(dev(c)),
                      ln=(None, None, 1e-6), act="silu")
-    check_feats(host(y), want, "Co=512 LN")
+    check_feats(host(y), want, "Co=512 LN", "bf16")
 
 
 @pytest.mark.parametrize("variant,dt", [("umma", "f16"), ("umma", "bf16"), ("simt", "f32")])
 def test_subdivision_conv_and_up_tail(sp, variant, dt):
     """conv1 -> C2S for kept children only, then LN -> SiLU -> conv2 -> skip, against the unfused chain."""
     rng = np.random.default_rng(21)
-    n, Ci, Cc = 500, 64, 32
+    n, Ci, Cc = 500, 128, 64
     c = random_coords(rng, n, 9)
     x = rounded(rng.standard_normal((n, Ci)), dt)
     keep = rng.random((n, 8)) < 0.45
@@ -213,9 +222,9 @@ def test_subdivision_conv_and_up_tail(sp, variant, dt):
     hc_d = sp.subdiv_conv(xd, dev(w1, TD[dt]), dev(b1, TD[dt]), lv, variant=variant)
     check_feats(host(hc_d), hc, "subdivision conv")
     h_d = sp.subdiv_conv(xd, dev(w1, TD[dt]), dev(b1, TD[dt]), lv, ln=(None, None, 1e-6), act="silu", variant=variant)
-    check_feats(host(h_d), h, "subdivision conv + LN + SiLU")
+    check_feats(host(h_d), h, "subdivision conv + LN + SiLU", dt)
     out = sp.subm_conv(h_d, dev(w2, TD[dt]), dev(b2, TD[dt]), lv.nb, skip=(xd, lv.src, rep), variant=variant)
-    check_feats(host(out), want, "up-block tail")
+    check_feats(host(out), want, "up-block tail", dt)
     # the unfused operators give the same rows
     g = sp.gather_rows(dev(h_full, TD[dt]), lv.src, Cc)
     assert np.array_equal(host(g), hc)
@@ -231,11 +240,11 @@ def test_row_ops(sp):
         b = rng.standard_normal(96).astype(np.float32)
         want = oracle.round_to(oracle.layer_norm(x, g, b, 1e-5), dt)
         got = host(sp.layer_norm(dev(x, TD[dt]), dev(g), dev(b), 1e-5))
-        check_feats(got, want, f"layer_norm {dt}")
+        check_feats(got, want, f"layer_norm {dt}", dt)
         for kind in ("silu", "gelu", "gelu_tanh"):
             want = oracle.round_to(oracle.act(x, kind), dt)
             got = host(sp.act_(dev(x, TD[dt]), kind))
-            check_feats(got, want, f"{kind} {dt}")
+            check_feats(got, want, f"{kind} {dt}", dt)
         got = host(sp.add_(dev(x, TD[dt]), dev(r, TD[dt])))
         assert np.array_equal(got, oracle.round_to(x + r, dt))
 

@@ -168,7 +168,7 @@ def test_golden_integer_maps_bit_exact():
 @needs_gold
 def test_golden_features_within_tolerance():
     G = np.load(GOLD)
-    for tag, Ci, Co in (("f0", 64, 64), ("f1", 32, 96), ("f2", 128, 256)):
+    for tag, Ci, Co in (("f0", 64, 64), ("f1", 64, 96), ("f2", 128, 256)):
         c, x = G[f"{tag}_coords"], G[f"{tag}_x"].astype(np.float32)
         w = _w(Co, Ci, 7, G[f"{tag}_w_sha"])
         b = G[f"{tag}_b"].astype(np.float32) if f"{tag}_b" in G else None
@@ -179,7 +179,7 @@ def test_golden_features_within_tolerance():
     _close(oracle.conv_block(x, w, b, nbr, "f16", ln=(G["b0_g"], G["b0_be"], 1e-6), act_kind="gelu", residual=x), G["b0_y_ln_gelu_res"])
     _close(oracle.conv_block(x, w, b, nbr, "f16", ln=(None, None, 1e-6), act_kind="silu"), G["b0_y_ln_silu"])
     c, x, sub = G["u0_coords"], G["u0_x"].astype(np.float32), G["u0_sub"].astype(np.float32)
-    Ci, Cc = 64, 32
+    Ci, Cc = 128, 64
     w1, w2 = _w(8 * Cc, Ci, 9, G["u0_w1_sha"]), _w(Cc, Cc, 10, G["u0_w2_sha"])
     cc, src = oracle.subdivide(c, sub > 0)
     hc = oracle.gather_rows(oracle.conv_block(x, w1, G["u0_b1"].astype(np.float32), oracle.build_neighbors(c)[0], "f16"), src, Cc)

@@ -246,7 +246,8 @@ def subdivide(parent: SpConvCache, sub: torch.Tensor, want_sorted: bool = False)
     ctx.check(ctx.lib.t2sc_subdivide_count(ctx.h, _ptr(sub), _DT[sub.dtype], n, _ptr(off), ctypes.byref(m)))
     coords = torch.empty((m.value, 4), dtype=torch.int32, device=sub.device)
     src = torch.empty(m.value, dtype=torch.int32, device=sub.device)
-    ctx.check(ctx.lib.t2sc_subdivide_emit(ctx.h, _ptr(sub), _DT[sub.dtype], _ptr(parent.coords), _ptr(off), n, _ptr(coords), _ptr(src)))
+    if m.value:
+        ctx.check(ctx.lib.t2sc_subdivide_emit(ctx.h, _ptr(sub), _DT[sub.dtype], _ptr(parent.coords), _ptr(off), n, _ptr(coords), _ptr(src)))
     nb = build_neighbors(coords, 4096, 4096, 4096, want_sorted=want_sorted)
     return Level(coords, src, nb, parent)
 
