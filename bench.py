@@ -52,18 +52,21 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
 
-    def stop(self):
+    def stop(self, t0=None, t1=None):
+        """Summary of the samples taken between perf_counter times t0 and t1 (the timed region)."""
         if self.proc:
             self.proc.terminate()
+        rows = [r for t, r in self.rows if (t0 is None or t >= t0) and (t1 is None or t <= t1 + 0.05)]
+        self.rows = rows
         sm = [float(r[0]) for r in self.rows if len(r) >= 8 and r[0].replace(".", "").isdigit()]
         reasons = set()
         for r in self.rows:
@@ -193,14 +196,15 @@ def run_ours(args, rank, world, local_rank):
     T = st["active_taps"]
     flops = 2.0 * T * Ci * Co
     ev = lambda: torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(visible_gpu_index(local_rank))
+    if rank == 0:
+        sampler.start()                                 # nvidia-smi needs a moment to start: launch it before the warm-up
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    sampler = ClockSampler(visible_gpu_index(local_rank))
-    if rank == 0:
-        sampler.start()
+    t_region0 = time.perf_counter()
     l0 = ctx.launch_count()
     step_ms, conv_ms = [], []
     for _ in range(args.steps):
@@ -212,6 +216,7 @@ def run_ours(args, rank, world, local_rank):
         torch.cuda.synchronize()
         step_ms.append(a.elapsed_time(b)); conv_ms.append(c0.elapsed_time(c1))
     launches = ctx.launch_count() - l0
+    t_region1 = time.perf_counter()
     ctx.device_status()
     # end to end through the host-buffer entry point: H2D of coords / features / weights, map, conv, D2H of y
     e2e_ms = []
@@ -222,7 +227,7 @@ def run_ours(args, rank, world, local_rank):
         t1 = time.perf_counter()
         if i >= 2:
             e2e_ms.append((t1 - t0) * 1e3)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_region0, t_region1) if rank == 0 else None
     total, conv_total, e2e_total = sum(step_ms), sum(conv_ms), (sum(e2e_ms) / len(e2e_ms) if e2e_ms else float("nan"))
     if world > 1:
         t = torch.tensor([total, conv_total, e2e_total, flops, n], dtype=torch.float64, device=dev)
@@ -277,7 +282,7 @@ def run_ours(args, rank, world, local_rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg5"])

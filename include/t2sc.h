@@ -73,14 +73,16 @@ int t2sc_gather_rows(t2sc_ctx* ctx, const void* x, const int32_t* src, int64_t m
 int t2sc_add_skip(t2sc_ctx* ctx, void* h, const void* x, const int32_t* src, int64_t m, int Co, int Cin, int rep, int dtype);
 
 /* ---- execution plan for one neighbour map (replaces the scheduling half of SpConvCache: `sorted`
- * and valid(), src/spconv.h:6-11).  Orders the output rows so that rows of one 128-row tile share
+ * and valid(), src/spconv.h:6-11).  Orders the output rows so that rows of one tile share
  * most taps, and records each tile's tap mask.  `src` = NULL plans a submanifold conv over the n_rows
  * rows of nbr/gray; src [m] (from t2sc_subdivide_emit) plans the 2x-subdivision conv: m child rows,
  * each using its parent's neighbour row and the weight rows of its slot.  block_rows > 0 keeps the
- * ordering local to runs of that many caller rows (cache locality on large maps); 0 = library default.
+ * ordering local to runs of that many caller rows (cache locality on large maps); 0 = library default
+ * (one global sort up to 262,144 rows, runs of 65,536 rows above).
+  * tile_rows is 128 or 256 (0 = library default 128; 256: two 128-row accumulators share every weight slab).
  * The plan borrows nbr and src: they must outlive it. */
 int t2sc_plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_t* gray, int64_t n_rows,
-                     const int32_t* src, int64_t m, int64_t block_rows, t2sc_plan** out);
+                     const int32_t* src, int64_t m, int64_t block_rows, int tile_rows, t2sc_plan** out);
 int t2sc_plan_destroy(t2sc_ctx* ctx, t2sc_plan* plan);
 /* tiles, sum over tiles of rows*popcount(tile mask), sum over rows of popcount(row mask) (syncs) */
 int t2sc_plan_stats(t2sc_ctx* ctx, t2sc_plan* plan, int64_t* tiles, int64_t* computed_taps, int64_t* active_taps);

@@ -117,11 +117,11 @@ def test_subdivide_bit_exact(sp):
 
 def test_plan_is_a_permutation_with_covering_masks(sp):
     c = scenes.config1_sphere()
-    cache = sp.build_neighbors(dev(c), block_rows=4096)
+    cache = sp.build_neighbors(dev(c), block_rows=4096, tile_rows=256)
     order = host(cache.plan.order())
     assert np.array_equal(np.sort(order), np.arange(c.shape[0]))
     st = cache.plan.stats()
-    assert st["tiles"] == (c.shape[0] + 127) // 128
+    assert st["tiles"] == (c.shape[0] + 255) // 256
     assert st["active_taps"] == 259166 and st["computed_taps"] >= st["active_taps"]
 
 
@@ -145,10 +145,11 @@ def test_subm_conv_matches_oracle(sp, variant, dt, n, res, Ci, Co):
     c, x, w, b = conv_case(rng, n, res, Ci, Co, dt)
     nbr = oracle.build_neighbors(c)[0]
     want = oracle.conv_block(x, w, b, nbr, dt)
-    cache = sp.build_neighbors(dev(c))
-    y = sp.subm_conv(dev(x, TD[dt]), dev(w, TD[dt]), dev(b, TD[dt]), cache, variant=variant)
-    cache.ctx.device_status()
-    check_feats(host(y), want, f"{variant} {dt} {n} {Ci}->{Co}")
+    for tile_rows in (256, 128):           # both schedules: two 128-row accumulators per weight slab, or one
+        cache = sp.build_neighbors(dev(c), tile_rows=tile_rows)
+        y = sp.subm_conv(dev(x, TD[dt]), dev(w, TD[dt]), dev(b, TD[dt]), cache, variant=variant)
+        cache.ctx.device_status()
+        check_feats(host(y), want, f"{variant} {dt} {n} {Ci}->{Co} tile {tile_rows}")
 
 
 def test_subm_conv_config1_fp32(sp):
@@ -186,10 +187,22 @@ def test_fused_layernorm_wide_falls_back_to_row_pass(sp):
     rng = np.random.default_rng(12)
     c, x, w, b = conv_case(rng, 600, 9, 64, 512, "bf16")
     nbr = oracle.build_neighbors(c)[0]
+    bf = torch.bfloat16
+    cache = sp.build_neighbors(dev(c))
+    y0 = host(sp.subm_conv(dev(x, bf), dev(w, bf), dev(b, bf), cache))
+    check_feats(y0, oracle.conv_block(x, w, b, nbr, "bf16"), "Co=512 conv")
+    y = sp.subm_conv(dev(x, bf), dev(w, bf), dev(b, bf), cache, ln=(None, None, 1e-6), act="silu")
+    # stage-wise with teacher forcing (the reference checks each stage on reference inputs the same way): the oracle's
+    # LN -> SiLU applied to THIS conv output must match to one rounding step; end to end a one-ulp flip in the conv
+    # output is amplified by 1/sigma of the row, so only the mean is held to the specification there
+    ln_o = oracle.round_to(oracle.layer_norm(y0, None, None, 1e-6), "bf16")
+    forced = oracle.round_to(oracle.act(ln_o, "silu"), "bf16")
+    binade = lambda a: 2.0 ** np.floor(np.log2(np.maximum(np.abs(a), 2.0 ** -126)))
+    err = np.abs(host(y) - forced)
+    # one rounding step of the LayerNorm output (SiLU's slope is at most 1.1) plus one of the result
+    assert (err <= ULP["bf16"] * (1.1 * binade(ln_o) + binade(forced))).all()
     want = oracle.conv_block(x, w, b, nbr, "bf16", ln=(None, None, 1e-6), act_kind="silu")
-    y = sp.subm_conv(dev(x, torch.bfloat16), dev(w, torch.bfloat16), dev(b, torch.bfloat16), sp.build_neighbors(dev(c)),
-                     ln=(None, None, 1e-6), act="silu")
-    check_feats(host(y), want, "Co=512 LN", "bf16")
+    assert np.abs(host(y) - want).sum() / np.abs(want).sum() <= MEAN_REL and np.abs(host(y) - want).max() <= 4 * MAX_ABS
 
 
 @pytest.mark.parametrize("variant,dt", [("umma", "f16"), ("umma", "bf16"), ("simt", "f32")])

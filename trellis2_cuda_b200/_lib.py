@@ -38,7 +38,7 @@ SYMBOLS = [
     ("t2sc_subdivide_emit", _i32, [_vp, _vp, _i32, _vp, _vp, _i64, _vp, _vp]),
     ("t2sc_gather_rows", _i32, [_vp, _vp, _vp, _i64, _i32, _i32, _vp]),
     ("t2sc_add_skip", _i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32]),
-    ("t2sc_plan_create", _i32, [_vp, _vp, _vp, _i64, _vp, _i64, _i64, _pp]),
+    ("t2sc_plan_create", _i32, [_vp, _vp, _vp, _i64, _vp, _i64, _i64, _i32, _pp]),
     ("t2sc_plan_destroy", _i32, [_vp, _vp]),
     ("t2sc_plan_stats", _i32, [_vp, _vp, _pi64, _pi64, _pi64]),
     ("t2sc_plan_order", _i32, [_vp, _vp, _vp]),

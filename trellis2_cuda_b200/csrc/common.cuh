@@ -37,6 +37,7 @@ struct t2sc_plan {
   int* ntiles = nullptr;        // device: realised tile count (<= max_tiles)
   unsigned long long* stats = nullptr;  // device [2]: computed taps, active taps
   i64 max_tiles = 0;
+  int tile_rows = 256;           // 128 or 256
 };
 
 int t2sc_fail(t2sc_ctx* ctx, int code, const char* fmt, ...);

@@ -4,7 +4,7 @@
 // tcgen05 kernel does not take (Ci not a multiple of 64, Co not a multiple of 32).  It computes the
 // operator of src/spconv.cu:91-150 (trellis2-cuda): y[i,co] = sum over the tile's taps, ascending, of
 // x[nbr[i,v],:] . w[co,v,:], fp32 accumulation, absent neighbours contributing zeros.
-// One CTA = one 128-row plan tile x 64 output channels; 256 threads, 8x4 outputs each; K in chunks of 16.
+// One CTA = 128 rows of a plan tile x 64 output channels; 256 threads, 8x4 outputs each; K in chunks of 16.
 #include "common.cuh"
 
 namespace {
@@ -35,17 +35,19 @@ template <class T>
 __global__ void __launch_bounds__(256) k_conv_simt(const T* __restrict__ x, const T* __restrict__ w, const uint32_t* __restrict__ nbr,
                                                    const int* __restrict__ order, const int* __restrict__ src,
                                                    const PlanTile* __restrict__ tiles, const int* __restrict__ ntiles,
-                                                   EpiDev ep, T* __restrict__ y, int Ci, int Co) {
-  if ((int)blockIdx.x >= *ntiles) return;
+                                                   EpiDev ep, T* __restrict__ y, int Ci, int Co, int subs) {
+  const int tile_id = blockIdx.x / subs, sub = blockIdx.x - tile_id * subs;      // plan tiles of 256 rows are two CTAs
+  if (tile_id >= *ntiles) return;
   __shared__ __align__(16) float As[BK][LDA];
   __shared__ __align__(16) float Bs[BK][LDB];
   __shared__ int s_out[BM];
   __shared__ int s_nrow[BM];
-  const PlanTile tile = tiles[blockIdx.x];
+  const PlanTile tile = tiles[tile_id];
+  if (sub * BM >= tile.rows) return;
   const int tid = threadIdx.x, co0 = blockIdx.y * BN;
   const i64 wrow0 = (i64)tile.wbase * Co;
   if (tid < BM) {
-    int r = tid < tile.rows ? order[tile.start + tid] : -1;
+    int r = sub * BM + tid < tile.rows ? order[tile.start + sub * BM + tid] : -1;
     s_out[tid] = r;
     s_nrow[tid] = r < 0 ? -1 : (src ? (src[r] >> 3) : r);
   }
@@ -162,13 +164,14 @@ int conv_simt_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const 
                      int dtype, int Ci, int Co) {
   T2_REQ(ctx, Ci % BK == 0, "Ci=%d", Ci);
   T2_CUDA(ctx, cudaSetDevice(ctx->device));
-  dim3 grid((unsigned)plan->max_tiles, (unsigned)cdiv_i(Co, BN));
+  const int subs = plan->tile_rows / BM;
+  dim3 grid((unsigned)(plan->max_tiles * subs), (unsigned)cdiv_i(Co, BN));
   if (dtype == T2SC_F32)
-    k_conv_simt<float><<<grid, 256, 0, ctx->stream>>>((const float*)x, (const float*)w, plan->nbr, plan->order, plan->src, plan->tiles, plan->ntiles, ep, (float*)y, Ci, Co);
+    k_conv_simt<float><<<grid, 256, 0, ctx->stream>>>((const float*)x, (const float*)w, plan->nbr, plan->order, plan->src, plan->tiles, plan->ntiles, ep, (float*)y, Ci, Co, subs);
   else if (dtype == T2SC_F16)
-    k_conv_simt<__half><<<grid, 256, 0, ctx->stream>>>((const __half*)x, (const __half*)w, plan->nbr, plan->order, plan->src, plan->tiles, plan->ntiles, ep, (__half*)y, Ci, Co);
+    k_conv_simt<__half><<<grid, 256, 0, ctx->stream>>>((const __half*)x, (const __half*)w, plan->nbr, plan->order, plan->src, plan->tiles, plan->ntiles, ep, (__half*)y, Ci, Co, subs);
   else
-    k_conv_simt<__nv_bfloat16><<<grid, 256, 0, ctx->stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, plan->nbr, plan->order, plan->src, plan->tiles, plan->ntiles, ep, (__nv_bfloat16*)y, Ci, Co);
+    k_conv_simt<__nv_bfloat16><<<grid, 256, 0, ctx->stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, plan->nbr, plan->order, plan->src, plan->tiles, plan->ntiles, ep, (__nv_bfloat16*)y, Ci, Co, subs);
   T2_LAUNCHED(ctx);
   return T2SC_OK;
 }

@@ -4,22 +4,28 @@
 // present in its tile, y[row, co] += x[nbr[row, v], :] . w[co, v, :].  The reference runs 32-64 row tiles
 // through mma.sync with register-staged copies; this kernel is organised around the Blackwell units:
 //
-//   * persistent CTAs, one per SM, walk (128-row plan tile x BN output channels) work items;
+//   * persistent CTAs, one per SM, walk (plan tile x BN output channels) work items.  A plan tile is MH
+//     128-row halves (MH = 1 or 2); each half has its own TMEM accumulator and all halves consume the
+//     same weight slab, which halves the L2 -> SM weight traffic of the 128-row schedule;
 //   * warps 0-3 gather the A operand: one 16-byte cp.async per (row, 8 channels), zero-filled for absent
-//     neighbours, written straight into the 128-byte-swizzled K-major layout tcgen05 reads.  The tile's
-//     slice of the neighbour map is staged in shared memory once per tile, not re-read per step;
+//     neighbours, written straight into the 128-byte-swizzled K-major layout tcgen05 reads.  (TMA
+//     tile::gather4 was measured for this job and moves 128-byte rows three times slower.)
+//   * warp 5 feeds them neighbour indices through a small ring, one slot per (tile, tap), running ahead
+//     across tile boundaries so that a new tile starts without a chain of dependent loads;
 //   * warp 4 streams the B operand (the tap's [BN x 64] weight slab) with a 3-D TMA tile load from the
 //     weights in their checkpoint layout [Co,27,Ci] - no re-layout, no cluster multicast;
-//   * warp 5 issues tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM accumulators and releases smem
-//     stages / publishes accumulators with tcgen05.commit;
-//   * warps 6-9 drain the other accumulator with tcgen05.ld and apply the fused epilogue (bias, LayerNorm,
-//     activation, residual, skip) with the reference's rounding points, one thread per output row, and
-//     scatter rows back to the caller's order.
+//   * warp 6 issues tcgen05.mma (M=128, N=BN, K=16) per half into TMEM and releases smem stages /
+//     publishes accumulators with tcgen05.commit; when 2*MH*BN <= 512 columns the accumulators are double
+//     buffered so the epilogue of one tile overlaps the main loop of the next;
+//   * 4*MH epilogue warps drain the accumulators with tcgen05.ld and apply the fused epilogue (bias,
+//     LayerNorm, activation, residual, skip) with the reference's rounding points, one thread per output
+//     row, and scatter rows back to the caller's order.
 //
 // Every mbarrier wait is bounded: a wait that runs out sets the context's status word, the CTA stops
 // blocking, drains and frees its TMEM; the host reports T2SC_ERR_DEVICE.
 #include "common.cuh"
 #include <cuda.h>
+#include <cstdlib>
 
 namespace {
 
@@ -27,22 +33,25 @@ constexpr int TILE_M = 128;
 constexpr int KCH = 64;                      // channels per pipeline step = one 128-byte swizzle row
 constexpr int A_BYTES = TILE_M * 128;
 constexpr int NUM_PROD_THREADS = 128;
-constexpr int WARP_TMA = 4, WARP_MMA = 5, WARP_EPI0 = 6;
-constexpr int NTHREADS = 320;
+constexpr int WARP_TMA = 4, WARP_IDX = 5, WARP_MMA = 6, WARP_EPI0 = 7;
+constexpr int IDX_SLOTS = 8;
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // ~2 s at boost clock
 constexpr int SMEM_BUDGET = 227 * 1024;
 
-__host__ __device__ constexpr int stage_bytes(int BN) { return A_BYTES + BN * 128; }
-__host__ __device__ constexpr int aux_bytes() { return TILE_M * 27 * 4 + TILE_M * 4 + 256; }
-__host__ __device__ constexpr int num_stages(int BN) {
-  int s = (SMEM_BUDGET - 1024 - aux_bytes()) / stage_bytes(BN);
+__host__ __device__ constexpr int num_threads(int MH) { return (7 + 4 * MH) * 32; }
+__host__ __device__ constexpr int stage_bytes(int BN, int MH) { return MH * A_BYTES + BN * 128; }
+__host__ __device__ constexpr int aux_bytes(int MH) { return IDX_SLOTS * MH * TILE_M * 4 + 512; }
+__host__ __device__ constexpr int num_stages(int BN, int MH) {
+  int s = (SMEM_BUDGET - 1024 - aux_bytes(MH)) / stage_bytes(BN, MH);
   return s > 8 ? 8 : s;
 }
+__host__ __device__ constexpr int num_acc_bufs(int BN, int MH) { return 2 * MH * BN <= 512 ? 2 : 1; }
 
 struct ConvArgs {
   const void* x; void* y; const uint32_t* nbr; const int* order; const int* src;
   const PlanTile* tiles; const int* ntiles; int* status;
   int Ci, Co, n_cot, is_bf16;
+  int dbg_skip;      // measurement aid (T2SC_DEBUG_SKIP): 1 = no A gather, 2 = no B load, 4 = no MMA; results are then invalid
   EpiDev ep;
 };
 
@@ -77,6 +86,10 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32
 // arrive on `bar` once all cp.async issued so far by this thread have landed (pending count +1 now, -1 then)
 __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+// the arrival itself, delivered once all cp.async issued so far by this thread have landed
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm, int c0, int c1, int c2, uint32_t bar) {
@@ -133,28 +146,33 @@ template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t v) { retu
 template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v)); }
 
 // ------------------------------------------------------------------------------------------ kernel
-template <int BN, class T>
-__global__ void __launch_bounds__(NTHREADS, 1) k_conv_umma(const __grid_constant__ CUtensorMap tmw, const ConvArgs a) {
-  constexpr int S = num_stages(BN);
-  constexpr int STAGE = stage_bytes(BN);
+// Warp roles: 0-3 gather A (cp.async), 4 weights (TMA), 5 neighbour-index ring, 6 MMA issue + TMEM owner,
+// 7.. epilogue (4 warps per 128-row half).
+template <int BN, int MH, class T>
+__global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_constant__ CUtensorMap tmw, const ConvArgs a) {
+  constexpr int S = num_stages(BN, MH);
+  constexpr int STAGE = stage_bytes(BN, MH);
   constexpr int B_BYTES = BN * 128;
-  constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  constexpr int NB = num_acc_bufs(BN, MH);            // accumulator buffers, each MH halves of BN columns
+  constexpr int TMEM_COLS = NB * MH * BN < 32 ? 32 : NB * MH * BN;
+  constexpr int ROWS = MH * TILE_M;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint32_t* nbr_s = (uint32_t*)(smem + S * STAGE);
-  int* nrow_s = (int*)(nbr_s + TILE_M * 27);
-  uint64_t* bars = (uint64_t*)(nrow_s + TILE_M);     // full[S] empty[S] accf[2] acce[2]
-  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * S + 4);
+  uint32_t* ring = (uint32_t*)(smem + S * STAGE);      // IDX_SLOTS x ROWS neighbour indices, one slot per (tile, tap)
+  uint64_t* bars = (uint64_t*)(ring + IDX_SLOTS * ROWS);   // full[S] empty[S] accf[2] acce[2] iready[IDX_SLOTS] ifree[IDX_SLOTS]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * S + 4 + 2 * IDX_SLOTS);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const uint32_t smem_base = smem_u32(smem);
-  const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * S, bar_accf = bar_empty + 8 * S, bar_acce = bar_accf + 16;
+  const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * S, bar_accf = bar_empty + 8 * S, bar_acce = bar_accf + 16,
+                 bar_iready = bar_acce + 16, bar_ifree = bar_iready + 8 * IDX_SLOTS;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, NUM_PROD_THREADS + 1); mbar_init(bar_empty + 8 * s, 1); }
-    for (int b = 0; b < 2; b++) { mbar_init(bar_accf + 8 * b, 1); mbar_init(bar_acce + 8 * b, 128); }
+    for (int b = 0; b < 2; b++) { mbar_init(bar_accf + 8 * b, 1); mbar_init(bar_acce + 8 * b, 128 * MH); }
+    for (int r = 0; r < IDX_SLOTS; r++) { mbar_init(bar_iready + 8 * r, 32); mbar_init(bar_ifree + 8 * r, NUM_PROD_THREADS); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -173,43 +191,33 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_conv_umma(const __grid_constant
   const int nchunk = a.Ci / KCH;
 
   if (warp < 4) {
-    // ===================================================================== A producer (gather)
+    // ===================================================================== A producer: gather rows into the swizzled tile
     const T* x = (const T*)a.x;
     const int t = threadIdx.x, jbase = t >> 3, c16 = t & 7;
     const uint32_t dst_thread = (uint32_t)(jbase * 128 + ((c16 ^ (jbase & 7)) << 4));   // (jbase + 16 i) & 7 == jbase & 7
-    uint32_t it = 0; int cur_tile = -1;
+    uint32_t it = 0, iit = 0;
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
-      const int tile_id = item / a.n_cot;
-      const PlanTile tile = a.tiles[tile_id];
-      if (tile_id != cur_tile) {
-        cur_tile = tile_id;
-        int nr = -1;
-        if (t < tile.rows) { int r = a.order[tile.start + t]; nr = a.src ? (a.src[r] >> 3) : r; }
-        nrow_s[t] = nr;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        for (int e = t; e < TILE_M * 27; e += NUM_PROD_THREADS) {
-          int j = e / 27, v = e - j * 27, r = nrow_s[j];
-          nbr_s[e] = r < 0 ? NBR_EMPTY : __ldg(a.nbr + (i64)r * 27 + v);
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-      }
-      for (uint32_t mk = tile.mask; mk; mk &= mk - 1) {
-        const int v = __ffs(mk) - 1;
-        uint32_t idx[8];
+      const PlanTile tile = a.tiles[item / a.n_cot];
+      for (uint32_t mk = tile.mask; mk; mk &= mk - 1, iit++) {
+        const uint32_t slot = iit % IDX_SLOTS, iph = (iit / IDX_SLOTS) & 1;
+        mbar_wait(bar_iready + 8 * slot, iph, abort_flag, a.status, 32);
+        uint32_t idx[8 * MH];       // rows jbase + 16 i; rows 128.. are the second half, stored right behind the first
 #pragma unroll
-        for (int i = 0; i < 8; i++) idx[i] = nbr_s[(jbase + 16 * i) * 27 + v];
+        for (int i = 0; i < 8 * MH; i++) idx[i] = ring[slot * ROWS + jbase + 16 * i];
+        mbar_arrive(bar_ifree + 8 * slot);
         for (int c = 0; c < nchunk; c++, it++) {
           const uint32_t s = it % S, ph = (it / S) & 1;
           mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, a.status, 1);
           const uint32_t dst = smem_base + s * STAGE + dst_thread;
           const T* xs = x + c * KCH + c16 * 8;
+          if (!(a.dbg_skip & 1)) {
 #pragma unroll
-          for (int i = 0; i < 8; i++) {
-            const bool present = idx[i] != NBR_EMPTY;
-            cp_async16(dst + i * (16 * 128), present ? (const void*)(xs + (i64)idx[i] * a.Ci) : (const void*)x, present ? 16u : 0u);
+            for (int i = 0; i < 8 * MH; i++) {
+              const bool present = idx[i] != NBR_EMPTY;
+              cp_async16(dst + i * (16 * 128), present ? (const void*)(xs + (i64)idx[i] * a.Ci) : (const void*)x, present ? 16u : 0u);
+            }
           }
-          cp_async_arrive(bar_full + 8 * s);
-          mbar_arrive(bar_full + 8 * s);
+          cp_async_arrive_noinc(bar_full + 8 * s);      // this thread's arrival, delivered when its copies have landed
         }
       }
     }
@@ -227,11 +235,39 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_conv_umma(const __grid_constant
           const uint32_t s = it % S, ph = (it / S) & 1;
           mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, a.status, 2);
           if (lane == 0) {
-            mbar_arrive_expect_tx(bar_full + 8 * s, B_BYTES);
-            tma_load_3d(smem_base + s * STAGE + A_BYTES, &tmw, c * KCH, v, wrow, bar_full + 8 * s);
+            if (a.dbg_skip & 2) mbar_arrive(bar_full + 8 * s);
+            else {
+              mbar_arrive_expect_tx(bar_full + 8 * s, B_BYTES);
+              tma_load_3d(smem_base + s * STAGE + MH * A_BYTES, &tmw, c * KCH, v, wrow, bar_full + 8 * s);
+            }
           }
           __syncwarp();
         }
+      }
+    }
+  } else if (warp == WARP_IDX) {
+    // ===================================================================== neighbour indices, one ring slot per (tile, tap)
+    // Runs ahead of the gather warps across tile boundaries, so a new tile starts without a dependent-load bubble.
+    uint32_t iit = 0;
+    for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+      const PlanTile tile = a.tiles[item / a.n_cot];
+      int nr[4 * MH];
+#pragma unroll
+      for (int i = 0; i < 4 * MH; i++) {
+        const int j = lane + 32 * i;
+        nr[i] = -1;
+        if (j < tile.rows) { const int r = a.order[tile.start + j]; nr[i] = a.src ? (a.src[r] >> 3) : r; }
+      }
+      for (uint32_t mk = tile.mask; mk; mk &= mk - 1, iit++) {
+        const int v = __ffs(mk) - 1;
+        const uint32_t slot = iit % IDX_SLOTS, iph = (iit / IDX_SLOTS) & 1;
+        uint32_t val[4 * MH];
+#pragma unroll
+        for (int i = 0; i < 4 * MH; i++) val[i] = nr[i] < 0 ? NBR_EMPTY : __ldg(a.nbr + (i64)nr[i] * 27 + v);
+        mbar_wait(bar_ifree + 8 * slot, iph ^ 1, abort_flag, a.status, 64);
+#pragma unroll
+        for (int i = 0; i < 4 * MH; i++) ring[slot * ROWS + lane + 32 * i] = val[i];
+        mbar_arrive(bar_iready + 8 * slot);
       }
     }
   } else if (warp == WARP_MMA) {
@@ -241,20 +277,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_conv_umma(const __grid_constant
     for (int item = blockIdx.x; item < nitems; item += gridDim.x, acc_it++) {
       const int tile_id = item / a.n_cot;
       const PlanTile tile = a.tiles[tile_id];
-      const uint32_t buf = acc_it & 1, aph = (acc_it >> 1) & 1;
+      const uint32_t buf = acc_it % NB, aph = (acc_it / NB) & 1;
       mbar_wait(bar_acce + 8 * buf, aph ^ 1, abort_flag, a.status, 4);
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + buf * BN;
+      const uint32_t d_tmem = tmem_base + buf * (MH * BN);
+      const int halves = tile.rows > TILE_M ? MH : 1;
       const int ksteps = __popc(tile.mask) * nchunk;
       for (int k = 0; k < ksteps; k++, it++) {
         const uint32_t s = it % S, ph = (it / S) & 1;
         mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, 8);
         tc_fence_after();
         if (lane == 0) {
-          const uint64_t ad = umma_desc(smem_base + s * STAGE), bd = umma_desc(smem_base + s * STAGE + A_BYTES);
+          const uint64_t bd = umma_desc(smem_base + s * STAGE + MH * A_BYTES);
+          for (int h = 0; h < halves && !(a.dbg_skip & 4); h++) {
+            const uint64_t ad = umma_desc(smem_base + s * STAGE + h * A_BYTES);
 #pragma unroll
-          for (int kk = 0; kk < KCH / 16; kk++)      // +32 bytes along K inside the swizzle row = +2 in the address field
-            tc_mma(d_tmem, ad + 2 * kk, bd + 2 * kk, idesc, (k > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 0; kk < KCH / 16; kk++)    // +32 bytes along K inside the swizzle row = +2 in the address field
+              tc_mma(d_tmem + h * BN, ad + 2 * kk, bd + 2 * kk, idesc, (k > 0 || kk > 0) ? 1u : 0u);
+          }
           tc_commit(bar_empty + 8 * s);
         }
         __syncwarp();
@@ -266,19 +306,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_conv_umma(const __grid_constant
     // ===================================================================== epilogue
     T* y = (T*)a.y;
     const T* bias = (const T*)a.ep.bias; const T* res = (const T*)a.ep.residual; const T* skx = (const T*)a.ep.skip_x;
-    const int q = warp & 3, j = q * 32 + lane;
+    const int q = warp & 3, half = (warp - WARP_EPI0) >> 2, j = half * TILE_M + q * 32 + lane;
     uint32_t acc_it = 0;
     for (int item = blockIdx.x; item < nitems; item += gridDim.x, acc_it++) {
       const int tile_id = item / a.n_cot, cot = item - tile_id * a.n_cot;
       const PlanTile tile = a.tiles[tile_id];
-      const uint32_t buf = acc_it & 1, aph = (acc_it >> 1) & 1;
+      const uint32_t buf = acc_it % NB, aph = (acc_it / NB) & 1;
       const int orow = j < tile.rows ? a.order[tile.start + j] : -1;
       const int wcol0 = tile.wbase * a.Co + cot * BN;      // bias index of this item's first column
       int sp = 0, ss = 0;
       if (skx && orow >= 0) { int sv = a.ep.skip_src[orow]; sp = sv >> 3; ss = sv & 7; }
       mbar_wait(bar_accf + 8 * buf, aph, abort_flag, a.status, 16);
       tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (MH * BN) + half * BN;
       float mean = 0.f, rstd = 1.f;
       if (a.ep.ln) {      // whole row lives in this accumulator (n_cot == 1): two statistics passes over TMEM
         float sum = 0.f;
@@ -385,28 +425,28 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-template <int BN, class T>
+template <int BN, int MH, class T>
 int launch_bn(t2sc_ctx* ctx, const CUtensorMap& tm, const ConvArgs& args, i64 max_items) {
-  constexpr int smem = num_stages(BN) * stage_bytes(BN) + aux_bytes() + 1024;
-  static_assert(smem <= SMEM_BUDGET, "shared memory budget");
+  constexpr int smem = num_stages(BN, MH) * stage_bytes(BN, MH) + aux_bytes(MH) + 1024;
+  static_assert(smem <= SMEM_BUDGET && num_stages(BN, MH) >= 3, "shared memory budget");
   static bool attr_set[16] = {};
   if (!attr_set[ctx->device & 15]) {
-    T2_CUDA(ctx, cudaFuncSetAttribute(k_conv_umma<BN, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    T2_CUDA(ctx, cudaFuncSetAttribute(k_conv_umma<BN, MH, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set[ctx->device & 15] = true;
   }
   int grid = (int)(max_items < ctx->num_sms ? max_items : ctx->num_sms);
-  k_conv_umma<BN, T><<<grid, NTHREADS, smem, ctx->stream>>>(tm, args);
+  k_conv_umma<BN, MH, T><<<grid, num_threads(MH), smem, ctx->stream>>>(tm, args);
   T2_LAUNCHED(ctx);
   return T2SC_OK;
 }
 
-template <class T>
+template <int MH, class T>
 int launch_t(t2sc_ctx* ctx, int BN, const CUtensorMap& tm, const ConvArgs& args, i64 max_items) {
   switch (BN) {
-    case 256: return launch_bn<256, T>(ctx, tm, args, max_items);
-    case 128: return launch_bn<128, T>(ctx, tm, args, max_items);
-    case 64: return launch_bn<64, T>(ctx, tm, args, max_items);
-    default: return launch_bn<32, T>(ctx, tm, args, max_items);
+    case 256: return launch_bn<256, MH, T>(ctx, tm, args, max_items);
+    case 128: return launch_bn<128, MH, T>(ctx, tm, args, max_items);
+    case 64: return launch_bn<64, MH, T>(ctx, tm, args, max_items);
+    default: return launch_bn<32, MH, T>(ctx, tm, args, max_items);
   }
 }
 
@@ -424,7 +464,6 @@ bool conv_umma_supported(int dtype, int Ci, int Co, const EpiDev& ep) {
 
 int conv_umma_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const void* w, i64 w_rows, const EpiDev& ep, void* y,
                      int dtype, i64 n_in, int Ci, int Co) {
-  (void)n_in;
   T2_CUDA(ctx, cudaSetDevice(ctx->device));
   const int BN = pick_bn(Co);
   T2_REQ(ctx, BN > 0, "Co=%d", Co);
@@ -442,10 +481,14 @@ int conv_umma_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const 
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (cr != CUDA_SUCCESS) return t2sc_fail(ctx, T2SC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for weights [%lld,27,%d]", (int)cr, (long long)w_rows, Ci);
   ConvArgs args;
+  (void)n_in;
+  static const int dbg_skip = [] { const char* e = getenv("T2SC_DEBUG_SKIP"); return e ? atoi(e) : 0; }();
+  args.dbg_skip = dbg_skip;
   args.x = x; args.y = y; args.nbr = plan->nbr; args.order = plan->order; args.src = plan->src;
   args.tiles = plan->tiles; args.ntiles = plan->ntiles; args.status = ctx->status;
   args.Ci = Ci; args.Co = Co; args.n_cot = Co / BN; args.is_bf16 = dtype == T2SC_BF16; args.ep = ep;
   i64 max_items = plan->max_tiles * args.n_cot;
-  if (dtype == T2SC_BF16) return launch_t<__nv_bfloat16>(ctx, BN, tm, args, max_items);
-  return launch_t<__half>(ctx, BN, tm, args, max_items);
+  if (plan->tile_rows == 2 * TILE_M)
+    return dtype == T2SC_BF16 ? launch_t<2, __nv_bfloat16>(ctx, BN, tm, args, max_items) : launch_t<2, __half>(ctx, BN, tm, args, max_items);
+  return dtype == T2SC_BF16 ? launch_t<1, __nv_bfloat16>(ctx, BN, tm, args, max_items) : launch_t<1, __half>(ctx, BN, tm, args, max_items);
 }

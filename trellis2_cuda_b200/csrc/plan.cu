@@ -1,4 +1,4 @@
-// Execution plan: which output rows share a 128-row tile, and which taps each tile has to visit.
+// Execution plan: which output rows share a tile (128 or 256 rows), and which taps each tile has to visit.
 //
 // The reference schedules by a global stable sort of the gray->binary mask key and per-block tap lists
 // (src/spconv.cu:34,47-75 of trellis2-cuda).  Here the sort key is (weight group, run of block_rows caller
@@ -11,12 +11,20 @@
 
 namespace {
 
-constexpr int TILE = 128;
 
-__device__ __forceinline__ uint32_t gray_to_bin(uint32_t g) {
-  uint32_t b = g;
+// Sort key of a 27-bit tap mask.  The reference sorts by the gray->binary decode of the mask as it stands
+// (src/spconv.cu:34).  Here the bits are first reordered so that the taps that are most often absent on a
+// surface shell lead: the 8 corner taps, then the 12 edge taps, then the 6 face taps, then the centre.  Rows
+// that differ only in common taps then end up adjacent, which shrinks the union mask of a tile (measured on a
+// 218k-voxel shell: active/computed taps 0.833 -> 0.855 for 128-row tiles).
+__constant__ uint8_t TAP_RANK[27] = {0, 8, 1, 9, 20, 10, 2, 11, 3, 12, 21, 13, 22, 26, 23, 14, 24, 15, 4, 16, 5, 17, 25, 18, 6, 19, 7};
+__device__ __forceinline__ uint32_t mask_key(uint32_t g) {
+  uint32_t k = 0;
 #pragma unroll
-  for (int v = 1; v < 27; v++) b ^= g >> v;
+  for (int v = 0; v < 27; v++) k |= ((g >> v) & 1u) << (26 - TAP_RANK[v]);
+  uint32_t b = k;
+#pragma unroll
+  for (int v = 1; v < 27; v++) b ^= k >> v;
   return b;
 }
 
@@ -28,13 +36,13 @@ __global__ void k_plan_keys(const int* __restrict__ gray, const int* __restrict_
   int grp = 0; i64 nrow = i;
   if (src) { int s = src[i]; grp = s & 7; nrow = s >> 3; }
   unsigned long long blk = (unsigned long long)(i / block_rows);
-  keys[i] = ((unsigned long long)grp << (27 + block_bits)) | (blk << 27) | gray_to_bin((uint32_t)gray[nrow]);
+  keys[i] = ((unsigned long long)grp << (27 + block_bits)) | (blk << 27) | mask_key((uint32_t)gray[nrow]);
   iota[i] = (int)i;
   if (src) atomicAdd(&group_cnt[grp], 1);
 }
 
 // one thread: tile offsets of the (up to 8) groups
-__global__ void k_plan_groups(const int* __restrict__ group_cnt, int ngroups, i64 m, int* __restrict__ gmeta, int* __restrict__ ntiles) {
+__global__ void k_plan_groups(const int* __restrict__ group_cnt, int ngroups, i64 m, int TILE, int* __restrict__ gmeta, int* __restrict__ ntiles) {
   // gmeta[g] = first row of group g, gmeta[16+g] = first tile of group g
   int row = 0, tile = 0;
   for (int g = 0; g < ngroups; g++) {
@@ -48,7 +56,7 @@ __global__ void k_plan_groups(const int* __restrict__ group_cnt, int ngroups, i6
 
 // one warp per tile: extent, weight base, OR of the row masks; also the plan's tap statistics
 __global__ void k_plan_tiles(const int* __restrict__ gray, const int* __restrict__ src, const int* __restrict__ order,
-                             const int* __restrict__ gmeta, int ngroups, int co_per_group, const int* __restrict__ ntiles,
+                             const int* __restrict__ gmeta, int ngroups, int TILE, const int* __restrict__ ntiles,
                              PlanTile* __restrict__ tiles, unsigned long long* __restrict__ stats) {
   int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (t >= *ntiles) return;
@@ -70,23 +78,25 @@ __global__ void k_plan_tiles(const int* __restrict__ gray, const int* __restrict
     atomicAdd(&stats[0], (unsigned long long)rows * __popc(o));
     atomicAdd(&stats[1], (unsigned long long)act);
   }
-  (void)co_per_group;
 }
 
 }  // namespace
 
 extern "C" int t2sc_plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_t* gray, int64_t n_rows,
-                                const int32_t* src, int64_t m, int64_t block_rows, t2sc_plan** out) {
+                                const int32_t* src, int64_t m, int64_t block_rows, int tile_rows, t2sc_plan** out) {
   T2_REQ(ctx, ctx && out, "null context or out");
   *out = nullptr;
   T2_REQ(ctx, n_rows >= 0 && m >= 0 && m < (1ll << 30) && n_rows < (1ll << 30), "n_rows=%lld m=%lld", (long long)n_rows, (long long)m);
   if (!src) T2_REQ(ctx, m == n_rows, "a submanifold plan has one output row per neighbour row (m=%lld n_rows=%lld)", (long long)m, (long long)n_rows);
   T2_REQ(ctx, m == 0 || (nbr && gray), "null tensor");
   T2_CUDA(ctx, cudaSetDevice(ctx->device));
-  if (block_rows <= 0) block_rows = 1 << 16;
+  if (block_rows <= 0) block_rows = m <= (1 << 18) ? (m > 0 ? m : 1) : (1 << 16);   // small maps: one global sort; large: keep gathers L2-local
+  if (tile_rows == 0) tile_rows = 128;
+  T2_REQ(ctx, tile_rows == 128 || tile_rows == 256, "tile_rows=%d", tile_rows);
+  const int TILE = tile_rows;
   T2_REQ(ctx, (m + block_rows - 1) / block_rows < (1ll << 23), "block_rows=%lld too small for m=%lld", (long long)block_rows, (long long)m);
   t2sc_plan* p = new t2sc_plan();
-  p->n_out = m; p->n_rows = n_rows; p->nbr = nbr; p->src = src;
+  p->n_out = m; p->n_rows = n_rows; p->nbr = nbr; p->src = src; p->tile_rows = tile_rows;
   int ngroups = src ? 8 : 1;
   p->max_tiles = cdiv_i(m, TILE) + (src ? 8 : 0);
   unsigned long long *keys = nullptr, *keys2 = nullptr; int *iota = nullptr, *gcnt = nullptr, *gmeta = nullptr; void* tmp = nullptr;
@@ -116,9 +126,9 @@ extern "C" int t2sc_plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_
     PL(cub::DeviceRadixSort::SortPairs(nullptr, tb, keys, keys2, iota, p->order, (int)m, 0, end_bit, ctx->stream));
     PL(t2_alloc(ctx, (char**)&tmp, tb));
     PL(cub::DeviceRadixSort::SortPairs(tmp, tb, keys, keys2, iota, p->order, (int)m, 0, end_bit, ctx->stream));
-    k_plan_groups<<<1, 1, 0, ctx->stream>>>(gcnt, ngroups, m, gmeta, p->ntiles);
+    k_plan_groups<<<1, 1, 0, ctx->stream>>>(gcnt, ngroups, m, TILE, gmeta, p->ntiles);
     ctx->launches++; PL(cudaGetLastError());
-    k_plan_tiles<<<cdiv_i(p->max_tiles * 32, 256), 256, 0, ctx->stream>>>(gray, src, p->order, gmeta, ngroups, 0, p->ntiles, p->tiles, p->stats);
+    k_plan_tiles<<<cdiv_i(p->max_tiles * 32, 256), 256, 0, ctx->stream>>>(gray, src, p->order, gmeta, ngroups, TILE, p->ntiles, p->tiles, p->stats);
     ctx->launches++; PL(cudaGetLastError());
   }
 #undef PL

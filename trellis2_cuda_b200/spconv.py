@@ -94,11 +94,11 @@ def spconv_cfg(N: int, Ci: int, Co: int) -> SpConvCfg:
 
 
 class _Plan:
-    def __init__(self, ctx: Context, nbr, gray, src=None, block_rows: int = 0):
+    def __init__(self, ctx: Context, nbr, gray, src=None, block_rows: int = 0, tile_rows: int = 0):
         self.ctx, self.nbr, self.gray, self.src = ctx, nbr, gray, src     # keep the borrowed tensors alive
         m = src.shape[0] if src is not None else nbr.shape[0]
         h = ctypes.c_void_p()
-        ctx.check(ctx.lib.t2sc_plan_create(ctx.h, _ptr(nbr), _ptr(gray), nbr.shape[0], _ptr(src), m, block_rows, ctypes.byref(h)))
+        ctx.check(ctx.lib.t2sc_plan_create(ctx.h, _ptr(nbr), _ptr(gray), nbr.shape[0], _ptr(src), m, block_rows, tile_rows, ctypes.byref(h)))
         self.h, self.n_out = h, m
 
     def stats(self):
@@ -124,12 +124,12 @@ class SpConvCache:
     the uint32 map, -1 = 0xffffffff = absent), ``gray`` [N] presence mask, ``sorted`` [N] reference row
     order, ``valid(B1)`` -> (tap list, segment offsets).  ``plan`` is this build's schedule."""
 
-    def __init__(self, ctx, coords, nbr, gray, sorted_, block_rows=0):
+    def __init__(self, ctx, coords, nbr, gray, sorted_, block_rows=0, tile_rows=0):
         self.ctx, self.coords, self.N = ctx, coords, int(coords.shape[0])
         self.nbr, self.gray, self.sorted = nbr, gray, sorted_
         self.vk: dict = {}
         self._plan = None
-        self._block_rows = block_rows
+        self._block_rows, self._tile_rows = block_rows, tile_rows
 
     def valid(self, B1: int):
         if B1 not in self.vk:
@@ -146,13 +146,21 @@ class SpConvCache:
 
     @property
     def plan(self) -> _Plan:
+        return self.plan_for(256)
+
+    def plan_for(self, Co: int) -> _Plan:
+        """The schedule used for a conv with Co output channels: 128-row tiles (double-buffered accumulators)
+        for Co >= 256, 256-row tiles (two accumulators per weight slab) below, unless tile_rows was forced."""
+        tr = self._tile_rows or (128 if Co >= 256 else 256)
         if self._plan is None:
-            self._plan = _Plan(self.ctx, self.nbr, self.gray, None, self._block_rows)
-        return self._plan
+            self._plan = {}
+        if tr not in self._plan:
+            self._plan[tr] = _Plan(self.ctx, self.nbr, self.gray, None, self._block_rows, tr)
+        return self._plan[tr]
 
 
 def build_neighbors(coords: torch.Tensor, W: int = 4096, H: int = 4096, D: int = 4096, want_sorted: bool = True,
-                    block_rows: int = 0) -> SpConvCache:
+                    block_rows: int = 0, tile_rows: int = 0) -> SpConvCache:
     """coords int32 [N,4] = (b,x,y,z) -> SpConvCache (src/spconv.cu:38-54)."""
     _chk(coords, "coords", torch.int32, 2)
     if coords.shape[1] != 4:
@@ -163,7 +171,7 @@ def build_neighbors(coords: torch.Tensor, W: int = 4096, H: int = 4096, D: int =
     gray = torch.empty(n, dtype=torch.int32, device=coords.device)
     srt = torch.empty(n, dtype=torch.int32, device=coords.device) if want_sorted else None
     ctx.check(ctx.lib.t2sc_build_neighbors(ctx.h, _ptr(coords), n, W, H, D, _ptr(nbr), _ptr(gray), _ptr(srt)))
-    return SpConvCache(ctx, coords, nbr, gray, srt, block_rows)
+    return SpConvCache(ctx, coords, nbr, gray, srt, block_rows, tile_rows)
 
 
 def _epilogue(Co, dtype, bias, ln, act, residual, skip):
@@ -213,7 +221,7 @@ def subm_conv(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], c: Sp
     (``add_``), ``skip=(x_parent, src, rep)`` (``k_add_skip``)."""
     if x.shape[0] != c.N:
         raise T2scError(-1, f"spconv shapes: x has {x.shape[0]} rows, cache has {c.N}")
-    return _conv(c.ctx, c.plan, x, w, b, w.shape[0], ln, act, residual, skip, variant, out)
+    return _conv(c.ctx, c.plan_for(w.shape[0]), x, w, b, w.shape[0], ln, act, residual, skip, variant, out)
 
 
 @dataclasses.dataclass
@@ -229,7 +237,7 @@ class Level:
     @property
     def up_plan(self) -> _Plan:
         if self._up_plan is None:
-            self._up_plan = _Plan(self.parent.ctx, self.parent.nbr, self.parent.gray, self.src, 0)
+            self._up_plan = _Plan(self.parent.ctx, self.parent.nbr, self.parent.gray, self.src, 0, 256)
         return self._up_plan
 
 
