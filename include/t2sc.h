@@ -52,6 +52,24 @@ int t2sc_device_status(t2sc_ctx* ctx, int* status_host); /* syncs; non-zero = a 
 int t2sc_build_neighbors(t2sc_ctx* ctx, const int32_t* coords, int64_t n, int W, int H, int D,
                          uint32_t* nbr, int32_t* gray, int32_t* sorted);
 
+/* Neighbour maps for callers that must not allocate.  (No counterpart in the reference, whose
+ * build_neighbors always allocates.)  Same nbr / gray results as t2sc_build_neighbors, but the hash table is
+ * a fixed 2 MiB array that is part of the library image, so this call performs no cudaMalloc, cudaFree or
+ * pool allocation of any kind; it is meant for hosts that have given the whole device to an arena of their
+ * own, or that forbid allocation once start-up is over, where a cudaMalloc can fail or force a device-wide
+ * synchronisation.  Limits and rules:
+ *   - at most T2SC_STATIC_MAX_ROWS rows; more is refused with T2SC_ERR_UNSUPPORTED and a message;
+ *   - no `sorted` output (the reference row order needs sort scratch: use t2sc_build_neighbors for it);
+ *   - every GPU that loads the library carries the 2 MiB array until the process exits;
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress); make that
+ *     first call during start-up, before any stream capture;
+ *   - all calls on a device share the one array: it is cleared at the start of each call, and two calls
+ *     whose kernels overlap on the GPU (different streams or contexts) corrupt each other - serialise them.
+ * The context itself (t2sc_ctx_create) is made at start-up, when allocating is still allowed. */
+#define T2SC_STATIC_MAX_ROWS 65536
+int t2sc_build_neighbors_static(t2sc_ctx* ctx, const int32_t* coords, int64_t n, int W, int H, int D,
+                                uint32_t* nbr, int32_t* gray);
+
 /* Replaces SpConvCache::valid (src/spconv.cu:56-75).  seg [ceil(n/B1)+1] exclusive offsets, list
  * [27*ceil(n/B1)] ascending taps present in each block of B1 consecutive `sorted` rows; *total_host
  * receives seg[nb] (one host sync, as in the reference). */

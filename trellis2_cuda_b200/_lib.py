@@ -11,6 +11,7 @@ LIB_PATH = os.path.join(HERE, "libt2sc.so")
 F32, F16, BF16, U8 = 0, 1, 2, 5
 ACT_NONE, ACT_SILU, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2, 3
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_UMMA = 0, 1, 2
+STATIC_MAX_ROWS = 65536
 
 # every symbol include/t2sc.h declares: (name, restype, argtypes)
 _vp, _i32, _i64, _f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
@@ -33,6 +34,7 @@ SYMBOLS = [
     ("t2sc_launch_count", _i64, [_vp]),
     ("t2sc_device_status", _i32, [_vp, _pi32]),
     ("t2sc_build_neighbors", _i32, [_vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp]),
+    ("t2sc_build_neighbors_static", _i32, [_vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp]),
     ("t2sc_valid_taps", _i32, [_vp, _vp, _vp, _i64, _i32, _vp, _vp, _pi64]),
     ("t2sc_subdivide_count", _i32, [_vp, _vp, _i32, _i64, _vp, _pi64]),
     ("t2sc_subdivide_emit", _i32, [_vp, _vp, _i32, _vp, _vp, _i64, _vp, _vp]),

@@ -276,3 +276,39 @@ extern "C" int t2sc_add_skip(t2sc_ctx* ctx, void* h, const void* x, const int32_
   T2_LAUNCHED(ctx);
   return T2SC_OK;
 }
+
+
+// ------------------------------------------------------------------------------------------ allocation-free variant
+// The hash table of this variant is a fixed array inside the library image instead of pool memory.
+static __device__ __align__(256) unsigned char g_static_table[(size_t)2 * T2SC_STATIC_MAX_ROWS * sizeof(Slot)];
+static Slot* g_static_table_ptr[64] = {nullptr};      // device address of the array, per device, resolved on first use
+
+extern "C" int t2sc_build_neighbors_static(t2sc_ctx* ctx, const int32_t* coords, int64_t n, int W, int H, int D,
+                                           uint32_t* nbr, int32_t* gray) {
+  T2_REQ(ctx, ctx != nullptr, "null context");
+  T2_REQ(ctx, n >= 0, "n=%lld", (long long)n);
+  if (n > T2SC_STATIC_MAX_ROWS)
+    return t2sc_fail(ctx, T2SC_ERR_UNSUPPORTED, "t2sc_build_neighbors_static: %lld rows exceed the built-in table (at most %d rows); "
+                     "use t2sc_build_neighbors, which takes its table from the memory pool", (long long)n, T2SC_STATIC_MAX_ROWS);
+  if (n == 0) return T2SC_OK;
+  T2_REQ(ctx, coords && nbr && gray, "null tensor");
+  T2_REQ(ctx, (uintptr_t)coords % 16 == 0, "coords must be 16-byte aligned");
+  T2_REQ(ctx, W > 0 && H > 0 && D > 0, "grid extent %d %d %d", W, H, D);
+  T2_REQ(ctx, ctx->device >= 0 && ctx->device < 64, "device %d", ctx->device);
+  T2_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (!g_static_table_ptr[ctx->device]) {
+    // In host code the array's name is only a handle; the kernels need its address on THIS device.
+    void* p = nullptr;
+    T2_CUDA(ctx, cudaGetSymbolAddress(&p, g_static_table));
+    g_static_table_ptr[ctx->device] = (Slot*)p;
+  }
+  Slot* table = g_static_table_ptr[ctx->device];
+  uint32_t cap = 1; while (cap < 2u * (uint32_t)n) cap <<= 1;
+  // the array keeps the previous call's keys: every slot this call can probe is reset to "empty" first
+  T2_CUDA(ctx, cudaMemsetAsync(table, 0xff, (size_t)cap * sizeof(Slot), ctx->stream));
+  k_hash_insert<<<cdiv_i(n, 256), 256, 0, ctx->stream>>>((const int4*)coords, (int)n, W, H, D, table, cap - 1);
+  T2_LAUNCHED(ctx);
+  k_neighbors<<<cdiv_i(n, NB_ROWS), NB_THREADS, 0, ctx->stream>>>((const int4*)coords, (int)n, W, H, D, table, cap - 1, nbr, gray, nullptr);
+  T2_LAUNCHED(ctx);
+  return T2SC_OK;
+}
