@@ -52,6 +52,12 @@ int t2sc_device_status(t2sc_ctx* ctx, int* status_host); /* syncs; non-zero = a 
 int t2sc_build_neighbors(t2sc_ctx* ctx, const int32_t* coords, int64_t n, int W, int H, int D,
                          uint32_t* nbr, int32_t* gray, int32_t* sorted);
 
+/* Neighbour rows of the row range [row_lo, row_hi) against the hash of all n rows (global row indices in
+ * nbr): the map one rank of a Morton-range partition builds for the rows it owns.  The reference is
+ * single-GPU and has no counterpart; semantics per row are those of build_neighbors (src/spconv.cu:22-36). */
+int t2sc_build_neighbors_range(t2sc_ctx* ctx, const int32_t* coords, int64_t n, int W, int H, int D,
+                               int64_t row_lo, int64_t row_hi, uint32_t* nbr, int32_t* gray);
+
 /* Neighbour maps for callers that must not allocate.  (No counterpart in the reference, whose
  * build_neighbors always allocates.)  Same nbr / gray results as t2sc_build_neighbors, but the hash table is
  * a fixed 2 MiB array that is part of the library image, so this call performs no cudaMalloc, cudaFree or

@@ -284,6 +284,32 @@ def test_errors_are_reported_not_thrown_across_the_abi(sp):
         sp.subm_conv(torch.zeros((50, 64), device="cuda"), torch.zeros((64, 27, 64), device="cuda"), None, cache, variant="umma")
 
 
+def test_sharded_ranks_reproduce_the_single_gpu_conv(sp):
+    """Two and three Morton ranges emulated one after the other on one GPU: each range's local map (owned rows +
+    appended halo rows) through the unchanged conv kernel gives the same bits as the unsharded conv."""
+    from trellis2_cuda_b200 import sharding
+    c = scenes.config2_shell()[:60000]
+    n, C = c.shape[0], 128
+    cd = dev(c)
+    x = torch.randn(n, C, device="cuda").to(torch.bfloat16)
+    w = dev(scenes.kaiming_uniform_weight(C, C, 2), torch.bfloat16)
+    full = sp.build_neighbors(cd, want_sorted=False)
+    want = sp.subm_conv(x, w, None, full)
+    for world in (2, 3):
+        starts = sharding.partition(n, world)
+        for r in range(world):
+            lo, hi = starts[r], starts[r + 1]
+            nbr_g, gray = sp.build_neighbors_range(cd, lo, hi)
+            assert torch.equal(nbr_g, full.nbr[lo:hi]) and torch.equal(gray, full.gray[lo:hi])
+            halo, nbr_l, counts = sharding.local_map(nbr_g, lo, hi, starts)
+            assert counts[r] == 0 and 0 < halo.numel() < (hi - lo)
+            x_local = torch.cat([x[lo:hi], x[halo]], 0)               # what the halo exchange delivers
+            cache = sp.cache_from_map(cd[lo:hi], nbr_l.contiguous(), gray)
+            y = sp.subm_conv_local(x_local, w, None, cache)
+            assert torch.equal(y, want[lo:hi])
+    full.ctx.device_status()
+
+
 # ------------------------------------------------------------------------------------------ full-size properties
 def test_config2_properties_at_full_size(sp):
     """Configuration 2 (217,821 voxels, 256 -> 256, bf16): sampled rows against the oracle, plus

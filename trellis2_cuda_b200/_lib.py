@@ -34,6 +34,7 @@ SYMBOLS = [
     ("t2sc_launch_count", _i64, [_vp]),
     ("t2sc_device_status", _i32, [_vp, _pi32]),
     ("t2sc_build_neighbors", _i32, [_vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp]),
+    ("t2sc_build_neighbors_range", _i32, [_vp, _vp, _i64, _i32, _i32, _i32, _i64, _i64, _vp, _vp]),
     ("t2sc_build_neighbors_static", _i32, [_vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp]),
     ("t2sc_valid_taps", _i32, [_vp, _vp, _vp, _i64, _i32, _vp, _vp, _pi64]),
     ("t2sc_subdivide_count", _i32, [_vp, _vp, _i32, _i64, _vp, _pi64]),

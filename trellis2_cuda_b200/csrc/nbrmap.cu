@@ -278,6 +278,31 @@ extern "C" int t2sc_add_skip(t2sc_ctx* ctx, void* h, const void* x, const int32_
 }
 
 
+// Neighbour rows of the contiguous row range [row_lo, row_hi) only, against the hash of ALL n rows: what one rank
+// of a Morton-range partition needs (its owned rows, with global row indices in the map).  nbr [row_hi-row_lo, 27],
+// gray [row_hi-row_lo].  No counterpart in the reference, which is single-GPU.
+extern "C" int t2sc_build_neighbors_range(t2sc_ctx* ctx, const int32_t* coords, int64_t n, int W, int H, int D,
+                                          int64_t row_lo, int64_t row_hi, uint32_t* nbr, int32_t* gray) {
+  T2_REQ(ctx, ctx != nullptr, "null context");
+  T2_REQ(ctx, n >= 0 && n < (1ll << 30) && row_lo >= 0 && row_lo <= row_hi && row_hi <= n, "n=%lld range [%lld,%lld)", (long long)n, (long long)row_lo, (long long)row_hi);
+  if (row_hi == row_lo) return T2SC_OK;
+  T2_REQ(ctx, coords && nbr && gray, "null tensor");
+  T2_REQ(ctx, (uintptr_t)coords % 16 == 0, "coords must be 16-byte aligned");
+  T2_REQ(ctx, W > 0 && H > 0 && D > 0, "grid extent %d %d %d", W, H, D);
+  T2_CUDA(ctx, cudaSetDevice(ctx->device));
+  uint32_t cap = 1; while (cap < 2u * (uint32_t)n) cap <<= 1;
+  Slot* table = nullptr;
+  T2_CUDA(ctx, t2_alloc(ctx, &table, cap));
+  T2_CUDA(ctx, cudaMemsetAsync(table, 0xff, (size_t)cap * sizeof(Slot), ctx->stream));
+  k_hash_insert<<<cdiv_i(n, 256), 256, 0, ctx->stream>>>((const int4*)coords, (int)n, W, H, D, table, cap - 1);
+  T2_LAUNCHED(ctx);
+  const i64 m = row_hi - row_lo;
+  k_neighbors<<<cdiv_i(m, NB_ROWS), NB_THREADS, 0, ctx->stream>>>((const int4*)coords + row_lo, (int)m, W, H, D, table, cap - 1, nbr, gray, nullptr);
+  T2_LAUNCHED(ctx);
+  t2_free(ctx, table);
+  return T2SC_OK;
+}
+
 // ------------------------------------------------------------------------------------------ allocation-free variant
 // The hash table of this variant is a fixed array inside the library image instead of pool memory.
 static __device__ __align__(256) unsigned char g_static_table[(size_t)2 * T2SC_STATIC_MAX_ROWS * sizeof(Slot)];

@@ -174,6 +174,30 @@ def build_neighbors(coords: torch.Tensor, W: int = 4096, H: int = 4096, D: int =
     return SpConvCache(ctx, coords, nbr, gray, srt, block_rows, tile_rows)
 
 
+def build_neighbors_range(coords: torch.Tensor, row_lo: int, row_hi: int, W: int = 4096, H: int = 4096, D: int = 4096):
+    """Neighbour rows (global indices) and masks of rows [row_lo, row_hi) of `coords` -> (nbr int32 [m,27], gray [m])."""
+    _chk(coords, "coords", torch.int32, 2)
+    ctx = context(coords.device)
+    m = row_hi - row_lo
+    nbr = torch.empty((m, 27), dtype=torch.int32, device=coords.device)
+    gray = torch.empty(m, dtype=torch.int32, device=coords.device)
+    ctx.check(ctx.lib.t2sc_build_neighbors_range(ctx.h, _ptr(coords), coords.shape[0], W, H, D, row_lo, row_hi, _ptr(nbr), _ptr(gray)))
+    return nbr, gray
+
+
+def cache_from_map(coords_like: torch.Tensor, nbr: torch.Tensor, gray: torch.Tensor, block_rows: int = 0, tile_rows: int = 0) -> SpConvCache:
+    """Wraps an existing neighbour map (e.g. a rank's local map whose indices point into owned + halo rows)."""
+    return SpConvCache(context(nbr.device), coords_like, nbr, gray, None, block_rows, tile_rows)
+
+
+def subm_conv_local(x: torch.Tensor, w: torch.Tensor, b, c: SpConvCache, **kw) -> torch.Tensor:
+    """subm_conv whose input has MORE rows than the map (owned rows first, halo rows appended); output [c.N, Co]."""
+    if x.shape[0] < c.N:
+        raise T2scError(-1, f"spconv shapes: x has {x.shape[0]} rows, cache has {c.N}")
+    return _conv(c.ctx, c.plan_for(w.shape[0]), x, w, b, w.shape[0], kw.get("ln"), kw.get("act"), kw.get("residual"), kw.get("skip"),
+                 kw.get("variant", "auto"), kw.get("out"))
+
+
 def _epilogue(Co, dtype, bias, ln, act, residual, skip):
     e = _lib.Epilogue()
     keep = []
