@@ -310,6 +310,61 @@ def test_sharded_ranks_reproduce_the_single_gpu_conv(sp):
     full.ctx.device_status()
 
 
+def test_decoder_like_stack_layer_by_layer(sp):
+    """The residual-block stack of configuration 4 (conv -> LN -> GELU -> conv -> residual, then a 2x subdivision
+    conv halving the channels) over the first three levels of its voxel pyramid (3,727 -> 16,725 -> 57,120 voxels),
+    with reduced widths 256 -> 128 -> 64 so the CPU oracle stays fast.  Layer by layer with teacher forcing: every
+    layer is fed the library's own previous output, and sampled rows are compared with the oracle."""
+    lv = scenes.config4_levels(levels=3)
+    rng = np.random.default_rng(4)
+    dt, td = "bf16", torch.bfloat16
+    C = 256
+    coords = lv[0][0]
+    cache = sp.build_neighbors(dev(coords))
+    x = dev(rounded(rng.standard_normal((coords.shape[0], C)), dt), td)
+
+    def check_layer(y, x_in, w, b, nbr, what, **kw):
+        rows = np.random.default_rng(1).choice(y.shape[0], min(200, y.shape[0]), replace=False).astype(np.int32)
+        res = kw.pop("residual", None)
+        want = oracle.conv_block(host(x_in), host(w), host(b), nbr, dt, nrow=kw.pop("nrow", rows), residual=None if res is None else host(res)[rows], **kw)
+        check_feats(host(y)[rows], want, what, dt)
+
+    for level in range(3):
+        coords, flags = lv[level]
+        nbr = oracle.build_neighbors(coords, want_sorted=False)[0]
+        assert np.array_equal(host(cache.nbr).view(np.uint32), nbr)
+        for blk in range(2):
+            w1 = dev(rounded(scenes.kaiming_uniform_weight(C, C, 10 * level + blk), dt), td)
+            w2 = dev(rounded(scenes.kaiming_uniform_weight(C, C, 10 * level + blk + 5), dt), td)
+            b1 = dev(rounded(0.05 * rng.standard_normal(C), dt), td)
+            g = dev((1 + 0.1 * rng.standard_normal(C)).astype(np.float32))
+            be = dev((0.1 * rng.standard_normal(C)).astype(np.float32))
+            h = sp.subm_conv(x, w1, b1, cache, ln=(g, be, 1e-6), act="gelu")
+            h0 = sp.subm_conv(x, w1, b1, cache)                       # conv part alone against the oracle ...
+            check_layer(h0, x, w1, b1, nbr, f"L{level} B{blk} conv1")
+            rows = np.arange(0, h.shape[0], max(1, h.shape[0] // 200))
+            forced = oracle.round_to(oracle.act(oracle.round_to(oracle.layer_norm(host(h0)[rows], host(g), host(be), 1e-6), dt), "gelu"), dt)
+            check_feats(host(h)[rows], forced, f"L{level} B{blk} LN+GELU on the library's conv output", dt)   # ... and the fused tail on top of it
+            y = sp.subm_conv(h, w2, b1, cache, residual=x)
+            check_layer(y, h, w2, b1, nbr, f"L{level} B{blk} conv2+res", residual=x)
+            x = y
+        if flags is None or level == 2:
+            break
+        Cc = C // 2
+        level_next = sp.subdivide(cache, dev(flags))
+        assert np.array_equal(host(level_next.coords), lv[level + 1][0])
+        wu = dev(rounded(scenes.kaiming_uniform_weight(8 * Cc, C, 50 + level), dt), td)
+        bu = dev(rounded(0.05 * rng.standard_normal(8 * Cc), dt), td)
+        up = sp.subdiv_conv(x, wu, bu, level_next)
+        src = host(level_next.src)
+        rows = np.random.default_rng(2).choice(src.shape[0], 200, replace=False)
+        want = oracle.conv_block(host(x), host(wu), host(bu), nbr, dt, nrow=(src[rows] >> 3).astype(np.int32),
+                                 wsel=((src[rows] & 7) * Cc).astype(np.int32), Co=Cc)
+        check_feats(host(up)[rows], want, f"L{level} subdivision conv", dt)
+        x, cache, C = up, level_next.nb, Cc
+    cache.ctx.device_status()
+
+
 # ------------------------------------------------------------------------------------------ full-size properties
 def test_config2_properties_at_full_size(sp):
     """Configuration 2 (217,821 voxels, 256 -> 256, bf16): sampled rows against the oracle, plus

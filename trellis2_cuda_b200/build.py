@@ -27,12 +27,12 @@ def _deps_mtime() -> float:
     return max(os.path.getmtime(f) for f in files)
 
 
-def build_library(force: bool = False, verbose: bool = False) -> str:
+def build_library(force: bool = False, verbose: bool = False, profile_waits: bool = False) -> str:
     srcs = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
     if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= _deps_mtime():
         return LIB
     os.makedirs(OBJ, exist_ok=True)
-    extra = ["-Xptxas", "-v"] if verbose else []
+    extra = (["-Xptxas", "-v"] if verbose else []) + (["-DT2SC_PROFILE_WAITS"] if profile_waits else [])
 
     def cc(src):
         obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
@@ -52,4 +52,5 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build_library(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_library(force="--force" in sys.argv or "--profile-waits" in sys.argv, verbose="--verbose" in sys.argv,
+                        profile_waits="--profile-waits" in sys.argv))

@@ -34,7 +34,13 @@ constexpr int KCH = 64;                      // channels per pipeline step = one
 constexpr int A_BYTES = TILE_M * 128;
 constexpr int NUM_PROD_THREADS = 128;
 constexpr int WARP_TMA = 4, WARP_IDX = 5, WARP_MMA = 6, WARP_EPI0 = 7;
+#ifdef T2SC_PROFILE_WAITS
+constexpr bool kProfileWaits = true;     // diagnostic build (python -m trellis2_cuda_b200.build --profile-waits)
+#else
+constexpr bool kProfileWaits = false;
+#endif
 constexpr int IDX_SLOTS = 8;
+constexpr int IDX_ROUND = 4;          // taps whose index loads are issued together by the index warp
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // ~2 s at boost clock
 constexpr int SMEM_BUDGET = 227 * 1024;
 
@@ -51,7 +57,7 @@ struct ConvArgs {
   const void* x; void* y; const uint32_t* nbr; const int* order; const int* src;
   const PlanTile* tiles; const int* ntiles; int* status;
   int Ci, Co, n_cot, is_bf16;
-  int dbg_skip;      // measurement aid (T2SC_DEBUG_SKIP): 1 = no A gather, 2 = no B load, 4 = no MMA; results are then invalid
+  int dbg_skip;      // measurement aid (T2SC_DEBUG_SKIP): 1 = no A gather, 2 = no B load, 4 = no MMA (results are then invalid), 8 = CTA 0 prints where each role waited
   EpiDev ep;
 };
 
@@ -79,6 +85,13 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatil
   while (!mbar_try(bar, parity)) {
     if (*abort_flag || clock64() - t0 > WAIT_LIMIT_CYCLES) { *abort_flag = 1; atomicOr(status, code); return; }
   }
+}
+// measurement aid (T2SC_DEBUG_SKIP bit 3): waits that also add their duration to a per-role counter
+__device__ __forceinline__ void mbar_wait_t(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code, bool prof, long long& acc) {
+  if (!prof) { mbar_wait(bar, parity, abort_flag, status, code); return; }
+  long long t0 = clock64();
+  mbar_wait(bar, parity, abort_flag, status, code);
+  acc += clock64() - t0;
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -196,20 +209,22 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
     const int t = threadIdx.x, jbase = t >> 3, c16 = t & 7;
     const uint32_t dst_thread = (uint32_t)(jbase * 128 + ((c16 ^ (jbase & 7)) << 4));   // (jbase + 16 i) & 7 == jbase & 7
     uint32_t it = 0, iit = 0;
+    const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_idx = 0, w_empty = 0, w_cp = 0, w_arr = 0, t_role = clock64();
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
       const PlanTile tile = a.tiles[item / a.n_cot];
       for (uint32_t mk = tile.mask; mk; mk &= mk - 1, iit++) {
         const uint32_t slot = iit % IDX_SLOTS, iph = (iit / IDX_SLOTS) & 1;
-        mbar_wait(bar_iready + 8 * slot, iph, abort_flag, a.status, 32);
+        mbar_wait_t(bar_iready + 8 * slot, iph, abort_flag, a.status, 32, prof, w_idx);
         uint32_t idx[8 * MH];       // rows jbase + 16 i; rows 128.. are the second half, stored right behind the first
 #pragma unroll
         for (int i = 0; i < 8 * MH; i++) idx[i] = ring[slot * ROWS + jbase + 16 * i];
         mbar_arrive(bar_ifree + 8 * slot);
         for (int c = 0; c < nchunk; c++, it++) {
           const uint32_t s = it % S, ph = (it / S) & 1;
-          mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, a.status, 1);
+          mbar_wait_t(bar_empty + 8 * s, ph ^ 1, abort_flag, a.status, 1, prof, w_empty);
           const uint32_t dst = smem_base + s * STAGE + dst_thread;
           const T* xs = x + c * KCH + c16 * 8;
+          long long tc0 = prof ? clock64() : 0;
           if (!(a.dbg_skip & 1)) {
 #pragma unroll
             for (int i = 0; i < 8 * MH; i++) {
@@ -217,11 +232,16 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
               cp_async16(dst + i * (16 * 128), present ? (const void*)(xs + (i64)idx[i] * a.Ci) : (const void*)x, present ? 16u : 0u);
             }
           }
+          long long tc1 = prof ? clock64() : 0;
           cp_async_arrive_noinc(bar_full + 8 * s);      // this thread's arrival, delivered when its copies have landed
+          if (prof) { w_cp += tc1 - tc0; w_arr += clock64() - tc1; }
         }
       }
     }
     cp_async_wait_all();
+    if (prof && blockIdx.x == 0 && threadIdx.x == 0)
+      printf("[t2sc prof] gather: total %lld clk, wait index ring %lld, wait stage free %lld, cp.async issue %lld, arrive %lld, steps %u\n",
+             clock64() - t_role, w_idx, w_empty, w_cp, w_arr, it);
   } else if (warp == WARP_TMA) {
     // ===================================================================== B producer (weights by TMA)
     uint32_t it = 0;
@@ -248,45 +268,83 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
   } else if (warp == WARP_IDX) {
     // ===================================================================== neighbour indices, one ring slot per (tile, tap)
     // Runs ahead of the gather warps across tile boundaries, so a new tile starts without a dependent-load bubble.
+    // The loads of one round of IDX_ROUND taps are all in flight before the previous round is handed over, and the
+    // next tile's row numbers are fetched while this tile's taps are served: the warp is never one load latency per tap.
+    constexpr int NR = 4 * MH;
     uint32_t iit = 0;
-    for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
-      const PlanTile tile = a.tiles[item / a.n_cot];
-      int nr[4 * MH];
+    const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_free = 0, w_load = 0, t_role = clock64();
+    auto rows_of = [&](int item, int* nr) {
+      if (item >= nitems) return;
+      const PlanTile tl = a.tiles[item / a.n_cot];
 #pragma unroll
-      for (int i = 0; i < 4 * MH; i++) {
+      for (int i = 0; i < NR; i++) {
         const int j = lane + 32 * i;
         nr[i] = -1;
-        if (j < tile.rows) { const int r = a.order[tile.start + j]; nr[i] = a.src ? (a.src[r] >> 3) : r; }
+        if (j < tl.rows) { const int r = a.order[tl.start + j]; nr[i] = a.src ? (a.src[r] >> 3) : r; }
       }
-      for (uint32_t mk = tile.mask; mk; mk &= mk - 1, iit++) {
-        const int v = __ffs(mk) - 1;
+    };
+    auto load_round = [&](uint32_t (&val)[IDX_ROUND][NR], uint32_t& mk, const int* nr) {
+#pragma unroll
+      for (int q = 0; q < IDX_ROUND; q++) {
+        if (!mk) break;
+        const int v = __ffs(mk) - 1; mk &= mk - 1;
+#pragma unroll
+        for (int i = 0; i < NR; i++) val[q][i] = nr[i] < 0 ? NBR_EMPTY : __ldg(a.nbr + (i64)nr[i] * 27 + v);
+      }
+    };
+    auto retire_round = [&](const uint32_t (&val)[IDX_ROUND][NR], uint32_t& mk) {
+#pragma unroll
+      for (int q = 0; q < IDX_ROUND; q++) {
+        if (!mk) break;
+        mk &= mk - 1;
         const uint32_t slot = iit % IDX_SLOTS, iph = (iit / IDX_SLOTS) & 1;
-        uint32_t val[4 * MH];
+        mbar_wait_t(bar_ifree + 8 * slot, iph ^ 1, abort_flag, a.status, 64, prof, w_free);
+        if (prof) { long long t0 = clock64(); volatile uint32_t sink = val[q][0]; (void)sink; w_load += clock64() - t0; }
 #pragma unroll
-        for (int i = 0; i < 4 * MH; i++) val[i] = nr[i] < 0 ? NBR_EMPTY : __ldg(a.nbr + (i64)nr[i] * 27 + v);
-        mbar_wait(bar_ifree + 8 * slot, iph ^ 1, abort_flag, a.status, 64);
-#pragma unroll
-        for (int i = 0; i < 4 * MH; i++) ring[slot * ROWS + lane + 32 * i] = val[i];
+        for (int i = 0; i < NR; i++) ring[slot * ROWS + lane + 32 * i] = val[q][i];
         mbar_arrive(bar_iready + 8 * slot);
+        iit++;
       }
+    };
+    int nr[NR], nr_next[NR];
+    rows_of(blockIdx.x, nr);
+    for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+      const PlanTile tile = a.tiles[item / a.n_cot];
+      rows_of(item + gridDim.x, nr_next);                      // in flight while this tile is served
+      uint32_t mk_load = tile.mask, mk_ret = tile.mask;
+      uint32_t va[IDX_ROUND][NR], vb[IDX_ROUND][NR];
+      load_round(va, mk_load, nr);
+      while (mk_ret) {
+        load_round(vb, mk_load, nr);
+        retire_round(va, mk_ret);
+        if (!mk_ret) break;
+        load_round(va, mk_load, nr);
+        retire_round(vb, mk_ret);
+      }
+#pragma unroll
+      for (int i = 0; i < NR; i++) nr[i] = nr_next[i];
     }
+    if (prof && blockIdx.x == 0 && lane == 0)
+      printf("[t2sc prof] index warp: total %lld clk, wait slot free %lld, wait own loads %lld, slots %u\n", clock64() - t_role, w_free, w_load, iit);
   } else if (warp == WARP_MMA) {
     // ===================================================================== MMA issuer
     const uint32_t idesc = umma_idesc(BN, a.is_bf16);
     uint32_t it = 0, acc_it = 0;
+    const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_full = 0, w_acc = 0, w_issue = 0, w_commit = 0, t_role = clock64();
     for (int item = blockIdx.x; item < nitems; item += gridDim.x, acc_it++) {
       const int tile_id = item / a.n_cot;
       const PlanTile tile = a.tiles[tile_id];
       const uint32_t buf = acc_it % NB, aph = (acc_it / NB) & 1;
-      mbar_wait(bar_acce + 8 * buf, aph ^ 1, abort_flag, a.status, 4);
+      mbar_wait_t(bar_acce + 8 * buf, aph ^ 1, abort_flag, a.status, 4, prof, w_acc);
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + buf * (MH * BN);
       const int halves = tile.rows > TILE_M ? MH : 1;
       const int ksteps = __popc(tile.mask) * nchunk;
       for (int k = 0; k < ksteps; k++, it++) {
         const uint32_t s = it % S, ph = (it / S) & 1;
-        mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, 8);
+        mbar_wait_t(bar_full + 8 * s, ph, abort_flag, a.status, 8, prof, w_full);
         tc_fence_after();
+        long long ti0 = prof ? clock64() : 0;
         if (lane == 0) {
           const uint64_t bd = umma_desc(smem_base + s * STAGE + MH * A_BYTES);
           for (int h = 0; h < halves && !(a.dbg_skip & 4); h++) {
@@ -295,19 +353,25 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
             for (int kk = 0; kk < KCH / 16; kk++)    // +32 bytes along K inside the swizzle row = +2 in the address field
               tc_mma(d_tmem + h * BN, ad + 2 * kk, bd + 2 * kk, idesc, (k > 0 || kk > 0) ? 1u : 0u);
           }
+          long long ti1 = prof ? clock64() : 0;
           tc_commit(bar_empty + 8 * s);
+          if (prof) { w_issue += ti1 - ti0; w_commit += clock64() - ti1; }
         }
         __syncwarp();
       }
       if (lane == 0) tc_commit(bar_accf + 8 * buf);
       __syncwarp();
     }
+    if (prof && blockIdx.x == 0 && lane == 0)
+      printf("[t2sc prof] mma: total %lld clk, wait stage full %lld, wait accumulator free %lld, mma issue %lld, commit %lld, steps %u, tiles %u\n",
+             clock64() - t_role, w_full, w_acc, w_issue, w_commit, it, acc_it);
   } else {
     // ===================================================================== epilogue
     T* y = (T*)a.y;
     const T* bias = (const T*)a.ep.bias; const T* res = (const T*)a.ep.residual; const T* skx = (const T*)a.ep.skip_x;
     const int q = warp & 3, half = (warp - WARP_EPI0) >> 2, j = half * TILE_M + q * 32 + lane;
     uint32_t acc_it = 0;
+    const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_accf = 0, t_role = clock64();
     for (int item = blockIdx.x; item < nitems; item += gridDim.x, acc_it++) {
       const int tile_id = item / a.n_cot, cot = item - tile_id * a.n_cot;
       const PlanTile tile = a.tiles[tile_id];
@@ -316,7 +380,7 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
       const int wcol0 = tile.wbase * a.Co + cot * BN;      // bias index of this item's first column
       int sp = 0, ss = 0;
       if (skx && orow >= 0) { int sv = a.ep.skip_src[orow]; sp = sv >> 3; ss = sv & 7; }
-      mbar_wait(bar_accf + 8 * buf, aph, abort_flag, a.status, 16);
+      mbar_wait_t(bar_accf + 8 * buf, aph, abort_flag, a.status, 16, prof, w_accf);
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (MH * BN) + half * BN;
       float mean = 0.f, rstd = 1.f;
@@ -397,6 +461,8 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
       tc_fence_before();
       mbar_arrive(bar_acce + 8 * buf);
     }
+    if (prof && blockIdx.x == 0 && warp == WARP_EPI0 && lane == 0)
+      printf("[t2sc prof] epilogue: total %lld clk, wait accumulator full %lld (busy %lld), tiles %u\n", clock64() - t_role, w_accf, clock64() - t_role - w_accf, acc_it);
   }
 
   tc_fence_before();
