@@ -152,7 +152,7 @@ extern "C" int t2sc_subm_conv_host(t2sc_ctx* ctx, const int32_t* coords_host, in
     HOST_TRY(cudaMemcpyAsync(b, bias_host, (size_t)Co * es, cudaMemcpyHostToDevice, ctx->stream));
   }
   if ((rc = t2sc_build_neighbors(ctx, coords, n, W, H, D, nbr, gray, nullptr)) != T2SC_OK) { cleanup(); return rc; }
-  if ((rc = t2sc_plan_create(ctx, nbr, gray, n, nullptr, n, 0, Co >= 256 ? 128 : 256, &plan)) != T2SC_OK) { cleanup(); return rc; }
+  if ((rc = t2sc_plan_create(ctx, nbr, gray, n, nullptr, n, 0, 0, &plan)) != T2SC_OK) { cleanup(); return rc; }
   t2sc_epilogue ep; memset(&ep, 0, sizeof(ep)); ep.bias = b;
   if ((rc = t2sc_subm_conv(ctx, plan, x, w, &ep, y, dtype, n, Ci, Co, T2SC_VARIANT_AUTO)) != T2SC_OK) { cleanup(); return rc; }
   HOST_TRY(cudaMemcpyAsync(y_host, y, (size_t)n * Co * es, cudaMemcpyDeviceToHost, ctx->stream));

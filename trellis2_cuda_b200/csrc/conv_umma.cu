@@ -40,7 +40,10 @@ constexpr bool kProfileWaits = true;     // diagnostic build (python -m trellis2
 constexpr bool kProfileWaits = false;
 #endif
 constexpr int IDX_SLOTS = 8;
-constexpr int IDX_ROUND = 4;          // taps whose index loads are issued together by the index warp
+#ifndef T2SC_IDX_ROUND
+#define T2SC_IDX_ROUND 1      // measured: 1 is as fast as 2 or 4 with 128-row tiles and faster with 256-row tiles
+#endif
+constexpr int IDX_ROUND = T2SC_IDX_ROUND;          // taps whose index loads are issued together by the index warp
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // ~2 s at boost clock
 constexpr int SMEM_BUDGET = 227 * 1024;
 
