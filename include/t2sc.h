@@ -32,7 +32,8 @@ enum { T2SC_ACT_NONE = 0, T2SC_ACT_SILU = 1, T2SC_ACT_GELU_TANH = 2, T2SC_ACT_GE
 /* status codes */
 enum { T2SC_OK = 0, T2SC_ERR_ARG = -1, T2SC_ERR_CUDA = -2, T2SC_ERR_UNSUPPORTED = -3, T2SC_ERR_DEVICE = -4 };
 /* conv kernel variants (t2sc_subm_conv `variant`): AUTO picks tcgen05 whenever the shape allows it */
-enum { T2SC_VARIANT_AUTO = 0, T2SC_VARIANT_SIMT = 1, T2SC_VARIANT_UMMA = 2 };
+enum { T2SC_VARIANT_AUTO = 0, T2SC_VARIANT_SIMT = 1, T2SC_VARIANT_UMMA = 2,
+       T2SC_VARIANT_UMMA_PAIR = 3 /* two-SM tcgen05 (cta_group::2): needs a 256-row plan and Co % 256 == 0 */ };
 
 /* ---- context.  Replaces the reference's process-wide stream and allocator (src/core.cu:20-40):
  * one context per device; `stream` is a cudaStream_t (NULL = the context creates its own

@@ -284,6 +284,25 @@ def test_errors_are_reported_not_thrown_across_the_abi(sp):
         sp.subm_conv(torch.zeros((50, 64), device="cuda"), torch.zeros((64, 27, 64), device="cuda"), None, cache, variant="umma")
 
 
+def test_two_sm_variant_equals_single_cta_kernel(sp):
+    """The cta_group::2 kernel (a CTA pair per 256-row tile, each CTA loading half of every weight slab) accumulates
+    every output element in the same order as the single-CTA kernel: results must be bit-identical, with and without
+    a fused epilogue, for one and for two 256-channel output slabs."""
+    rng = np.random.default_rng(8)
+    for n, res, Ci, Co in ((2000, 14, 64, 256), (700, 10, 128, 512), (9000, 24, 256, 256)):
+        c, x, w, b = conv_case(rng, n, res, Ci, Co, "bf16")
+        cache = sp.build_neighbors(dev(c), tile_rows=256)
+        xd, wd, bd = dev(x, torch.bfloat16), dev(w, torch.bfloat16), dev(b, torch.bfloat16)
+        kw = dict(act="silu", residual=xd) if Ci == Co else dict(ln=(None, None, 1e-6)) if Co == 256 else {}
+        y1 = sp.subm_conv(xd, wd, bd, cache, variant="umma", **kw)
+        y2 = sp.subm_conv(xd, wd, bd, cache, variant="umma_pair", **kw)
+        cache.ctx.device_status()
+        assert torch.equal(y1, y2)
+        check_feats(host(sp.subm_conv(xd, wd, bd, cache, variant="umma_pair")), oracle.conv_block(x, w, b, oracle.build_neighbors(c)[0], "bf16"), "two-SM variant")
+    with pytest.raises(sp.T2scError, match="two-SM"):
+        sp.subm_conv(xd, wd, bd, sp.build_neighbors(dev(c), tile_rows=128), variant="umma_pair")
+
+
 def test_sharded_ranks_reproduce_the_single_gpu_conv(sp):
     """Two and three Morton ranges emulated one after the other on one GPU: each range's local map (owned rows +
     appended halo rows) through the unchanged conv kernel gives the same bits as the unsharded conv."""

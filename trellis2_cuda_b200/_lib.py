@@ -10,7 +10,7 @@ LIB_PATH = os.path.join(HERE, "libt2sc.so")
 
 F32, F16, BF16, U8 = 0, 1, 2, 5
 ACT_NONE, ACT_SILU, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2, 3
-VARIANT_AUTO, VARIANT_SIMT, VARIANT_UMMA = 0, 1, 2
+VARIANT_AUTO, VARIANT_SIMT, VARIANT_UMMA, VARIANT_UMMA_PAIR = 0, 1, 2, 3
 STATIC_MAX_ROWS = 65536
 
 # every symbol include/t2sc.h declares: (name, restype, argtypes)

@@ -1,5 +1,6 @@
 // C-ABI entry points that are not kernels themselves: context, errors, conv dispatch, host-buffer call.
 #include "common.cuh"
+#include <cstdlib>
 
 static char g_create_err[512] = {0};
 
@@ -94,9 +95,14 @@ extern "C" int t2sc_subm_conv(t2sc_ctx* ctx, t2sc_plan* plan, const void* x, con
   bool umma_ok = conv_umma_supported(dtype, Ci, Co, e);
   if (variant == T2SC_VARIANT_UMMA && !umma_ok)
     return t2sc_fail(ctx, T2SC_ERR_UNSUPPORTED, "tcgen05 variant needs fp16/bf16, Ci %% 64 == 0, Co %% 32 == 0 (Ci=%d Co=%d dtype=%d)", Ci, Co, dtype);
-  bool use_umma = variant == T2SC_VARIANT_UMMA || (variant == T2SC_VARIANT_AUTO && umma_ok);
+  bool use_umma = variant == T2SC_VARIANT_UMMA || variant == T2SC_VARIANT_UMMA_PAIR || (variant == T2SC_VARIANT_AUTO && umma_ok);
   // LayerNorm needs the whole output row in one CTA: fused on the tcgen05 path for Co <= 256, else a second pass
   bool fuse_all = use_umma && (!e.ln || Co <= 256);
+  static const bool pair_mode = [] { const char* v = getenv("T2SC_CTA_PAIR"); return v && atoi(v) != 0; }();
+  if (variant == T2SC_VARIANT_UMMA_PAIR && !conv_umma2_supported(plan, dtype, Ci, Co, e))
+    return t2sc_fail(ctx, T2SC_ERR_UNSUPPORTED, "two-SM tcgen05 variant needs fp16/bf16, a 256-row plan, Ci %% 64 == 0, Co %% 256 == 0 (Ci=%d Co=%d tile_rows=%d)", Ci, Co, plan->tile_rows);
+  if (variant == T2SC_VARIANT_UMMA_PAIR || (fuse_all && pair_mode && variant != T2SC_VARIANT_SIMT && conv_umma2_supported(plan, dtype, Ci, Co, e)))
+    return conv_umma2_launch(ctx, plan, x, w, w_rows, e, y, dtype, Ci, Co);
   if (fuse_all) return conv_umma_launch(ctx, plan, x, w, w_rows, e, y, dtype, n_in, Ci, Co);
   EpiDev first = e, rest = e;
   if (e.ln) {  // conv + bias now; LN -> act -> residual -> skip in the row pass

@@ -23,143 +23,10 @@
 //
 // Every mbarrier wait is bounded: a wait that runs out sets the context's status word, the CTA stops
 // blocking, drains and frees its TMEM; the host reports T2SC_ERR_DEVICE.
-#include "common.cuh"
-#include <cuda.h>
-#include <cstdlib>
+#include "umma_common.cuh"
 
 namespace {
-
-constexpr int TILE_M = 128;
-constexpr int KCH = 64;                      // channels per pipeline step = one 128-byte swizzle row
-constexpr int A_BYTES = TILE_M * 128;
-constexpr int NUM_PROD_THREADS = 128;
-constexpr int WARP_TMA = 4, WARP_IDX = 5, WARP_MMA = 6, WARP_EPI0 = 7;
-#ifdef T2SC_PROFILE_WAITS
-constexpr bool kProfileWaits = true;     // diagnostic build (python -m trellis2_cuda_b200.build --profile-waits)
-#else
-constexpr bool kProfileWaits = false;
-#endif
-constexpr int IDX_SLOTS = 8;
-#ifndef T2SC_IDX_ROUND
-#define T2SC_IDX_ROUND 1      // measured: 1 is as fast as 2 or 4 with 128-row tiles and faster with 256-row tiles
-#endif
-constexpr int IDX_ROUND = T2SC_IDX_ROUND;          // taps whose index loads are issued together by the index warp
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // ~2 s at boost clock
-constexpr int SMEM_BUDGET = 227 * 1024;
-
-__host__ __device__ constexpr int num_threads(int MH) { return (7 + 4 * MH) * 32; }
-__host__ __device__ constexpr int stage_bytes(int BN, int MH) { return MH * A_BYTES + BN * 128; }
-__host__ __device__ constexpr int aux_bytes(int MH) { return IDX_SLOTS * MH * TILE_M * 4 + 512; }
-__host__ __device__ constexpr int num_stages(int BN, int MH) {
-  int s = (SMEM_BUDGET - 1024 - aux_bytes(MH)) / stage_bytes(BN, MH);
-  return s > 8 ? 8 : s;
-}
-__host__ __device__ constexpr int num_acc_bufs(int BN, int MH) { return 2 * MH * BN <= 512 ? 2 : 1; }
-
-struct ConvArgs {
-  const void* x; void* y; const uint32_t* nbr; const int* order; const int* src;
-  const PlanTile* tiles; const int* ntiles; int* status;
-  int Ci, Co, n_cot, is_bf16;
-  int dbg_skip;      // measurement aid (T2SC_DEBUG_SKIP): 1 = no A gather, 2 = no B load, 4 = no MMA (results are then invalid), 8 = CTA 0 prints where each role waited
-  EpiDev ep;
-};
-
-// ------------------------------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait.  After any wait in the CTA has given up, all later waits return at once.
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-  if (mbar_try(bar, parity)) return;
-  long long t0 = clock64();
-  while (!mbar_try(bar, parity)) {
-    if (*abort_flag || clock64() - t0 > WAIT_LIMIT_CYCLES) { *abort_flag = 1; atomicOr(status, code); return; }
-  }
-}
-// measurement aid (T2SC_DEBUG_SKIP bit 3): waits that also add their duration to a per-role counter
-__device__ __forceinline__ void mbar_wait_t(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code, bool prof, long long& acc) {
-  if (!prof) { mbar_wait(bar, parity, abort_flag, status, code); return; }
-  long long t0 = clock64();
-  mbar_wait(bar, parity, abort_flag, status, code);
-  acc += clock64() - t0;
-}
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-// arrive on `bar` once all cp.async issued so far by this thread have landed (pending count +1 now, -1 then)
-__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
-  asm volatile("cp.async.mbarrier.arrive.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
-// the arrival itself, delivered once all cp.async issued so far by this thread have landed
-__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm, int c0, int c1, int c2, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-               "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-               : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// K-major operand tile, rows of 128 bytes, 128-byte swizzle: 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);   // start address
-  d |= (uint64_t)1 << 16;                      // leading byte offset: unused with swizzled K-major, set to 1
-  d |= (uint64_t)(1024 >> 4) << 32;            // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;                      // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;                      // 128-byte swizzle
-  return d;
-}
-__host__ __device__ constexpr uint32_t umma_idesc(int N, int is_bf16) {
-  return (1u << 4)                              // D = fp32
-       | ((is_bf16 ? 1u : 0u) << 7)             // A format
-       | ((is_bf16 ? 1u : 0u) << 10)            // B format
-       | ((uint32_t)(N >> 3) << 17)             // N
-       | ((uint32_t)(TILE_M >> 4) << 24);       // M
-}
-
-template <class T> __device__ __forceinline__ uint32_t pack2(float a, float b);
-template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
-  __half2 h = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&h);
-}
-template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&h);
-}
-template <class T> __device__ __forceinline__ float2 unpack2(uint32_t v);
-template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t v) { return __half22float2(*reinterpret_cast<__half2*>(&v)); }
-template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v)); }
+using namespace umma;
 
 // ------------------------------------------------------------------------------------------ kernel
 // Warp roles: 0-3 gather A (cp.async), 4 weights (TMA), 5 neighbour-index ring, 6 MMA issue + TMEM owner,
@@ -370,8 +237,7 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
              clock64() - t_role, w_full, w_acc, w_issue, w_commit, it, acc_it);
   } else {
     // ===================================================================== epilogue
-    T* y = (T*)a.y;
-    const T* bias = (const T*)a.ep.bias; const T* res = (const T*)a.ep.residual; const T* skx = (const T*)a.ep.skip_x;
+    const bool has_skip = a.ep.skip_x != nullptr;
     const int q = warp & 3, half = (warp - WARP_EPI0) >> 2, j = half * TILE_M + q * 32 + lane;
     uint32_t acc_it = 0;
     const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_accf = 0, t_role = clock64();
@@ -382,85 +248,11 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
       const int orow = j < tile.rows ? a.order[tile.start + j] : -1;
       const int wcol0 = tile.wbase * a.Co + cot * BN;      // bias index of this item's first column
       int sp = 0, ss = 0;
-      if (skx && orow >= 0) { int sv = a.ep.skip_src[orow]; sp = sv >> 3; ss = sv & 7; }
+      if (has_skip && orow >= 0) { int sv = a.ep.skip_src[orow]; sp = sv >> 3; ss = sv & 7; }
       mbar_wait_t(bar_accf + 8 * buf, aph, abort_flag, a.status, 16, prof, w_accf);
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (MH * BN) + half * BN;
-      float mean = 0.f, rstd = 1.f;
-      if (a.ep.ln) {      // whole row lives in this accumulator (n_cot == 1): two statistics passes over TMEM
-        float sum = 0.f;
-        for (int cc = 0; cc < BN / 32; cc++) {
-          uint32_t r[32]; tc_ld32(taddr + cc * 32, r); tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; i++) {
-            float h = rnd<T>(__uint_as_float(r[i]));
-            if (bias) h = rnd<T>(h + to_f<T>(bias[wcol0 + cc * 32 + i]));
-            sum += h;
-          }
-        }
-        mean = sum / (float)BN;
-        float qs = 0.f;
-        for (int cc = 0; cc < BN / 32; cc++) {
-          uint32_t r[32]; tc_ld32(taddr + cc * 32, r); tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; i++) {
-            float h = rnd<T>(__uint_as_float(r[i]));
-            if (bias) h = rnd<T>(h + to_f<T>(bias[wcol0 + cc * 32 + i]));
-            float d = h - mean; qs += d * d;
-          }
-        }
-        rstd = rsqrtf(qs / (float)BN + a.ep.eps);
-      }
-      for (int cc = 0; cc < BN / 32; cc++) {
-        uint32_t r[32]; tc_ld32(taddr + cc * 32, r); tc_wait_ld();
-        if (orow < 0) continue;
-        const int col = cot * BN + cc * 32;
-        float h[32];
-#pragma unroll
-        for (int i = 0; i < 32; i++) {
-          float v = rnd<T>(__uint_as_float(r[i]));
-          if (bias) v = rnd<T>(v + to_f<T>(bias[wcol0 + cc * 32 + i]));
-          h[i] = v;
-        }
-        if (a.ep.ln) {
-#pragma unroll
-          for (int i = 0; i < 32; i++) {
-            float v = rstd * (h[i] - mean);
-            if (a.ep.gamma) v = a.ep.gamma[col + i] * v;
-            if (a.ep.beta) v = v + a.ep.beta[col + i];
-            h[i] = rnd<T>(v);
-          }
-        }
-        if (a.ep.act) {
-#pragma unroll
-          for (int i = 0; i < 32; i++) h[i] = rnd<T>(act_apply(h[i], a.ep.act));
-        }
-        if (res) {
-          const uint4* rp = (const uint4*)(res + (i64)orow * a.Co + col);
-#pragma unroll
-          for (int g = 0; g < 4; g++) {
-            uint4 rv = __ldg(rp + g); const uint32_t* w32 = (const uint32_t*)&rv;
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-              float2 f = unpack2<T>(w32[e]);
-              h[g * 8 + e * 2] = rnd<T>(h[g * 8 + e * 2] + f.x); h[g * 8 + e * 2 + 1] = rnd<T>(h[g * 8 + e * 2 + 1] + f.y);
-            }
-          }
-        }
-        if (skx) {
-          const T* sx = skx + (i64)sp * a.ep.skip_cin + ss * (a.ep.skip_cin / 8);
-#pragma unroll
-          for (int i = 0; i < 32; i++) h[i] = rnd<T>(h[i] + to_f<T>(sx[(col + i) / a.ep.skip_rep]));
-        }
-        uint4* yp = (uint4*)(y + (i64)orow * a.Co + col);
-#pragma unroll
-        for (int g = 0; g < 4; g++) {
-          uint4 o;
-          o.x = pack2<T>(h[g * 8 + 0], h[g * 8 + 1]); o.y = pack2<T>(h[g * 8 + 2], h[g * 8 + 3]);
-          o.z = pack2<T>(h[g * 8 + 4], h[g * 8 + 5]); o.w = pack2<T>(h[g * 8 + 6], h[g * 8 + 7]);
-          yp[g] = o;
-        }
-      }
+      epilogue_row<BN, T>(a, taddr, orow, cot, wcol0, sp, ss);
       tc_fence_before();
       mbar_arrive(bar_acce + 8 * buf);
     }

@@ -20,7 +20,7 @@ from ._lib import T2scError
 
 _DT = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.uint8: _lib.U8}
 _ACT = {None: 0, "none": 0, "silu": 1, "gelu_tanh": 2, "gelu": 3, "gelu_erf": 3}
-_VARIANT = {"auto": 0, "simt": 1, "umma": 2}
+_VARIANT = {"auto": 0, "simt": 1, "umma": 2, "umma_pair": 3}
 
 _contexts: dict = {}
 
