@@ -8,12 +8,22 @@ import os
 
 import numpy as np
 
-_SO = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_ref", "libt2ref.so")
-_lib = None
+_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_ref")
+_SO = os.path.join(_DIR, "libt2ref.so")
+_SO_DROPIN = os.path.join(_DIR, "libt2ref_dropin.so")      # the reference's decoder code on this repository's kernels
+_libs = {}
+_use_dropin = False
 
 
-def available() -> bool:
-    if not os.path.exists(_SO):
+def use_dropin(flag: bool) -> None:
+    """Route the calls below through libt2ref_dropin.so (reference sdec/ops/gemm/core + the t2sc binding in place of
+    the reference's spconv.cu) instead of the all-reference library."""
+    global _use_dropin
+    _use_dropin = bool(flag)
+
+
+def available(dropin: bool = False) -> bool:
+    if not os.path.exists(_SO_DROPIN if dropin else _SO):
         return False
     try:
         import torch
@@ -23,12 +33,12 @@ def available() -> bool:
 
 
 def lib():
-    global _lib
-    if _lib is None:
-        L = ctypes.CDLL(_SO)
+    key = _use_dropin
+    if key not in _libs:
+        L = ctypes.CDLL(_SO_DROPIN if key else _SO)
         L.ref_last_error.restype = ctypes.c_char_p
-        _lib = L
-    return _lib
+        _libs[key] = L
+    return _libs[key]
 
 
 def _p(a):

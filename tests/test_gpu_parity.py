@@ -284,6 +284,40 @@ def test_errors_are_reported_not_thrown_across_the_abi(sp):
         sp.subm_conv(torch.zeros((50, 64), device="cuda"), torch.zeros((64, 27, 64), device="cuda"), None, cache, variant="umma")
 
 
+def test_drop_in_for_the_reference_decoder_code(sp):
+    """The reference's own decoder sources (src/sdec.cu, src/ops.cu, src/gemm.cu, src/core.cu, compiled unchanged)
+    linked once with the reference's src/spconv.cu and once with the binding oracle/dropin_spconv.cu that calls this
+    library: the up-block tail (conv1 -> c2s -> gather -> LN -> SiLU -> conv2 -> skip) and a conv -> LN -> GELU ->
+    residual block must agree - maps bit for bit, features within the tolerance."""
+    from oracle import ref
+    if not (ref.available(False) and ref.available(True)):
+        pytest.skip("oracle/_ref libraries were not built (no checkout of the reference at build time)")
+    rng = np.random.default_rng(77)
+    c = random_coords(rng, 1500, 13)
+    out = {}
+    for dropin in (False, True):
+        ref.use_dropin(dropin)
+        nbr, gray, srt, seg, lst = ref.build_neighbors(c, 4096, 4096, 4096, B1=64)
+        Ci, Cc = 128, 64
+        r2 = np.random.default_rng(78)
+        x = r2.standard_normal((c.shape[0], Ci)).astype(np.float16)
+        sub = r2.standard_normal((c.shape[0], 8)).astype(np.float16)
+        w1 = scenes.kaiming_uniform_weight(8 * Cc, Ci, 9).astype(np.float16); b1 = (0.1 * r2.standard_normal(8 * Cc)).astype(np.float16)
+        w2 = scenes.kaiming_uniform_weight(Cc, Cc, 10).astype(np.float16); b2 = (0.1 * r2.standard_normal(Cc)).astype(np.float16)
+        hc, o = ref.up_tail(c, x, sub, w1, b1, w2, b2)
+        wb = scenes.kaiming_uniform_weight(Ci, Ci, 11).astype(np.float16)
+        g = (1 + 0.1 * r2.standard_normal(Ci)).astype(np.float32); be = (0.1 * r2.standard_normal(Ci)).astype(np.float32)
+        blk = ref.conv_block(c, x, wb, b1[:Ci], ln=(g, be, 1e-6), act=3, residual=x)
+        out[dropin] = (nbr, gray, srt, seg, lst, hc, o, blk)
+    ref.use_dropin(False)
+    a, b = out[False], out[True]
+    for i in range(5):
+        assert np.array_equal(a[i], b[i])
+    check_feats(b[5].astype(np.float32), a[5].astype(np.float32), "drop-in: gathered conv1 rows")
+    check_feats(b[6].astype(np.float32), a[6].astype(np.float32), "drop-in: up-block tail", "f16")
+    check_feats(b[7].astype(np.float32), a[7].astype(np.float32), "drop-in: conv-LN-GELU-residual block", "f16")
+
+
 def test_two_sm_variant_equals_single_cta_kernel(sp):
     """The cta_group::2 kernel (a CTA pair per 256-row tile, each CTA loading half of every weight slab) accumulates
     every output element in the same order as the single-CTA kernel: results must be bit-identical, with and without
