@@ -31,10 +31,13 @@ using namespace umma;
 // ------------------------------------------------------------------------------------------ kernel
 // Warp roles: 0-3 gather A (cp.async), 4 weights (TMA), 5 neighbour-index ring, 6 MMA issue + TMEM owner,
 // 7.. epilogue (4 warps per 128-row half).
-template <int BN, int MH, class T>
+// U = (tap, 64-channel chunk) units per pipeline stage: 1, or 2 for narrow layers, where one unit is too little work
+// for the cost of a barrier round trip.
+template <int BN, int MH, int U, class T>
 __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_constant__ CUtensorMap tmw, const ConvArgs a) {
-  constexpr int S = num_stages(BN, MH);
-  constexpr int STAGE = stage_bytes(BN, MH);
+  constexpr int UNIT = stage_bytes(BN, MH);          // one unit: MH gathered A halves + one weight slab
+  constexpr int STAGE = U * UNIT;
+  constexpr int S = num_stages(BN, MH, U);
   constexpr int B_BYTES = BN * 128;
   constexpr int NB = num_acc_bufs(BN, MH);            // accumulator buffers, each MH halves of BN columns
   constexpr int TMEM_COLS = NB * MH * BN < 32 ? 32 : NB * MH * BN;
@@ -55,7 +58,7 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, NUM_PROD_THREADS + 1); mbar_init(bar_empty + 8 * s, 1); }
     for (int b = 0; b < 2; b++) { mbar_init(bar_accf + 8 * b, 1); mbar_init(bar_acce + 8 * b, 128 * MH); }
-    for (int r = 0; r < IDX_SLOTS; r++) { mbar_init(bar_iready + 8 * r, 32); mbar_init(bar_ifree + 8 * r, NUM_PROD_THREADS); }
+    for (int r = 0; r < IDX_SLOTS; r++) { mbar_init(bar_iready + 8 * r, 1); mbar_init(bar_ifree + 8 * r, NUM_PROD_THREADS / 32); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -79,22 +82,26 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
     const int t = threadIdx.x, jbase = t >> 3, c16 = t & 7;
     const uint32_t dst_thread = (uint32_t)(jbase * 128 + ((c16 ^ (jbase & 7)) << 4));   // (jbase + 16 i) & 7 == jbase & 7
     uint32_t it = 0, iit = 0;
-    const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_idx = 0, w_empty = 0, w_cp = 0, w_arr = 0, t_role = clock64();
+    const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_idx = 0, w_empty = 0, t_role = clock64();
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
       const PlanTile tile = a.tiles[item / a.n_cot];
+      int q = 0; uint32_t st = 0;
       for (uint32_t mk = tile.mask; mk; mk &= mk - 1, iit++) {
         const uint32_t slot = iit % IDX_SLOTS, iph = (iit / IDX_SLOTS) & 1;
-        mbar_wait_t(bar_iready + 8 * slot, iph, abort_flag, a.status, 32, prof, w_idx);
+        const bool noring = a.dbg_skip & 128;
+        if (!noring) mbar_wait_t(bar_iready + 8 * slot, iph, abort_flag, a.status, 32, prof, w_idx);
         uint32_t idx[8 * MH];       // rows jbase + 16 i; rows 128.. are the second half, stored right behind the first
 #pragma unroll
         for (int i = 0; i < 8 * MH; i++) idx[i] = ring[slot * ROWS + jbase + 16 * i];
-        mbar_arrive(bar_ifree + 8 * slot);
-        for (int c = 0; c < nchunk; c++, it++) {
-          const uint32_t s = it % S, ph = (it / S) & 1;
-          mbar_wait_t(bar_empty + 8 * s, ph ^ 1, abort_flag, a.status, 1, prof, w_empty);
-          const uint32_t dst = smem_base + s * STAGE + dst_thread;
+        __syncwarp();
+        if (lane == 0 && !noring) mbar_arrive(bar_ifree + 8 * slot);       // one arrival per gather warp: arrivals on one barrier serialise
+        for (int c = 0; c < nchunk; c++) {
+          if (q == 0) {
+            st = it % S;
+            mbar_wait_t(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 1, prof, w_empty);
+          }
+          const uint32_t dst = smem_base + st * STAGE + q * UNIT + dst_thread;
           const T* xs = x + c * KCH + c16 * 8;
-          long long tc0 = prof ? clock64() : 0;
           if (!(a.dbg_skip & 1)) {
 #pragma unroll
             for (int i = 0; i < 8 * MH; i++) {
@@ -102,16 +109,14 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
               cp_async16(dst + i * (16 * 128), present ? (const void*)(xs + (i64)idx[i] * a.Ci) : (const void*)x, present ? 16u : 0u);
             }
           }
-          long long tc1 = prof ? clock64() : 0;
-          cp_async_arrive_noinc(bar_full + 8 * s);      // this thread's arrival, delivered when its copies have landed
-          if (prof) { w_cp += tc1 - tc0; w_arr += clock64() - tc1; }
+          if (++q == U) { cp_async_arrive_noinc(bar_full + 8 * st); q = 0; it++; }   // this thread's arrival, delivered when its copies have landed
         }
       }
+      if (q != 0) { cp_async_arrive_noinc(bar_full + 8 * st); it++; }                // last, partly filled stage of the item
     }
     cp_async_wait_all();
     if (prof && blockIdx.x == 0 && threadIdx.x == 0)
-      printf("[t2sc prof] gather: total %lld clk, wait index ring %lld, wait stage free %lld, cp.async issue %lld, arrive %lld, steps %u\n",
-             clock64() - t_role, w_idx, w_empty, w_cp, w_arr, it);
+      printf("[t2sc prof] gather: total %lld clk, wait index ring %lld, wait stage free %lld, stages %u\n", clock64() - t_role, w_idx, w_empty, it);
   } else if (warp == WARP_TMA) {
     // ===================================================================== B producer (weights by TMA)
     uint32_t it = 0;
@@ -119,21 +124,27 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
       const int tile_id = item / a.n_cot, cot = item - tile_id * a.n_cot;
       const PlanTile tile = a.tiles[tile_id];
       const int wrow = tile.wbase * a.Co + cot * BN;
+      const int nunits = __popc(tile.mask) * nchunk;
+      int q = 0, u = 0; uint32_t st = 0;
       for (uint32_t mk = tile.mask; mk; mk &= mk - 1) {
         const int v = __ffs(mk) - 1;
-        for (int c = 0; c < nchunk; c++, it++) {
-          const uint32_t s = it % S, ph = (it / S) & 1;
-          mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, a.status, 2);
-          if (lane == 0) {
-            if (a.dbg_skip & 2) mbar_arrive(bar_full + 8 * s);
-            else {
-              mbar_arrive_expect_tx(bar_full + 8 * s, B_BYTES);
-              tma_load_3d(smem_base + s * STAGE + MH * A_BYTES, &tmw, c * KCH, v, wrow, bar_full + 8 * s);
+        for (int c = 0; c < nchunk; c++, u++) {
+          if (q == 0) {
+            st = it % S;
+            mbar_wait(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 2);
+            const int nq = nunits - u < U ? nunits - u : U;
+            if (lane == 0) {
+              if (a.dbg_skip & 2) mbar_arrive(bar_full + 8 * st);
+              else mbar_arrive_expect_tx(bar_full + 8 * st, nq * B_BYTES);
             }
           }
+          if (lane == 0 && !(a.dbg_skip & 2))
+            tma_load_3d(smem_base + st * STAGE + q * UNIT + MH * A_BYTES, &tmw, c * KCH, v, wrow, bar_full + 8 * st);
           __syncwarp();
+          if (++q == U) { q = 0; it++; }
         }
       }
+      if (q != 0) it++;
     }
   } else if (warp == WARP_IDX) {
     // ===================================================================== neighbour indices, one ring slot per (tile, tap)
@@ -159,7 +170,7 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
         if (!mk) break;
         const int v = __ffs(mk) - 1; mk &= mk - 1;
 #pragma unroll
-        for (int i = 0; i < NR; i++) val[q][i] = nr[i] < 0 ? NBR_EMPTY : __ldg(a.nbr + (i64)nr[i] * 27 + v);
+        for (int i = 0; i < NR; i++) val[q][i] = (nr[i] < 0 || (a.dbg_skip & 32)) ? NBR_EMPTY : __ldg(a.nbr + (i64)nr[i] * 27 + v);
       }
     };
     auto retire_round = [&](const uint32_t (&val)[IDX_ROUND][NR], uint32_t& mk) {
@@ -172,13 +183,14 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
         if (prof) { long long t0 = clock64(); volatile uint32_t sink = val[q][0]; (void)sink; w_load += clock64() - t0; }
 #pragma unroll
         for (int i = 0; i < NR; i++) ring[slot * ROWS + lane + 32 * i] = val[q][i];
-        mbar_arrive(bar_iready + 8 * slot);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_iready + 8 * slot);
         iit++;
       }
     };
     int nr[NR], nr_next[NR];
     rows_of(blockIdx.x, nr);
-    for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+    for (int item = blockIdx.x; item < nitems && !(a.dbg_skip & 128); item += gridDim.x) {
       const PlanTile tile = a.tiles[item / a.n_cot];
       rows_of(item + gridDim.x, nr_next);                      // in flight while this tile is served
       uint32_t mk_load = tile.mask, mk_ret = tile.mask;
@@ -209,19 +221,22 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + buf * (MH * BN);
       const int halves = tile.rows > TILE_M ? MH : 1;
-      const int ksteps = __popc(tile.mask) * nchunk;
-      for (int k = 0; k < ksteps; k++, it++) {
+      const int nunits = __popc(tile.mask) * nchunk;
+      for (int u0 = 0; u0 < nunits; u0 += U, it++) {
         const uint32_t s = it % S, ph = (it / S) & 1;
         mbar_wait_t(bar_full + 8 * s, ph, abort_flag, a.status, 8, prof, w_full);
         tc_fence_after();
         long long ti0 = prof ? clock64() : 0;
         if (lane == 0) {
-          const uint64_t bd = umma_desc(smem_base + s * STAGE + MH * A_BYTES);
-          for (int h = 0; h < halves && !(a.dbg_skip & 4); h++) {
-            const uint64_t ad = umma_desc(smem_base + s * STAGE + h * A_BYTES);
+          const int nq = nunits - u0 < U ? nunits - u0 : U;
+          for (int q = 0; q < nq && !(a.dbg_skip & 4); q++) {
+            const uint64_t bd = umma_desc(smem_base + s * STAGE + q * UNIT + MH * A_BYTES);
+            for (int h = 0; h < halves; h++) {
+              const uint64_t ad = umma_desc(smem_base + s * STAGE + q * UNIT + h * A_BYTES);
 #pragma unroll
-            for (int kk = 0; kk < KCH / 16; kk++)    // +32 bytes along K inside the swizzle row = +2 in the address field
-              tc_mma(d_tmem + h * BN, ad + 2 * kk, bd + 2 * kk, idesc, (k > 0 || kk > 0) ? 1u : 0u);
+              for (int kk = 0; kk < KCH / 16; kk++)    // +32 bytes along K inside the swizzle row = +2 in the address field
+                tc_mma(d_tmem + h * BN, ad + 2 * kk, bd + 2 * kk, idesc, (u0 + q > 0 || kk > 0) ? 1u : 0u);
+            }
           }
           long long ti1 = prof ? clock64() : 0;
           tc_commit(bar_empty + 8 * s);
@@ -252,7 +267,7 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
       mbar_wait_t(bar_accf + 8 * buf, aph, abort_flag, a.status, 16, prof, w_accf);
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (MH * BN) + half * BN;
-      epilogue_row<BN, T>(a, taddr, orow, cot, wcol0, sp, ss);
+      if (!(a.dbg_skip & 64)) epilogue_row<BN, T>(a, taddr, orow, cot, wcol0, sp, ss);
       tc_fence_before();
       mbar_arrive(bar_acce + 8 * buf);
     }
@@ -286,19 +301,30 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-template <int BN, int MH, class T>
-int launch_bn(t2sc_ctx* ctx, const CUtensorMap& tm, const ConvArgs& args, i64 max_items) {
-  constexpr int smem = num_stages(BN, MH) * stage_bytes(BN, MH) + aux_bytes(MH) + 1024;
-  static_assert(smem <= SMEM_BUDGET && num_stages(BN, MH) >= 3, "shared memory budget");
+template <int BN, int MH, int U, class T>
+int launch_u(t2sc_ctx* ctx, const CUtensorMap& tm, const ConvArgs& args, i64 max_items) {
+  constexpr int smem = num_stages(BN, MH, U) * U * stage_bytes(BN, MH) + aux_bytes(MH) + 1024;
+  static_assert(smem <= SMEM_BUDGET && num_stages(BN, MH, U) >= 3, "shared memory budget");
   static bool attr_set[16] = {};
   if (!attr_set[ctx->device & 15]) {
-    T2_CUDA(ctx, cudaFuncSetAttribute(k_conv_umma<BN, MH, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    T2_CUDA(ctx, cudaFuncSetAttribute(k_conv_umma<BN, MH, U, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set[ctx->device & 15] = true;
   }
   int grid = (int)(max_items < ctx->num_sms ? max_items : ctx->num_sms);
-  k_conv_umma<BN, MH, T><<<grid, num_threads(MH), smem, ctx->stream>>>(tm, args);
+  k_conv_umma<BN, MH, U, T><<<grid, num_threads(MH), smem, ctx->stream>>>(tm, args);
   T2_LAUNCHED(ctx);
   return T2SC_OK;
+}
+
+// Two units per stage where a unit is small: 128-row tiles with at most 128 output channels per tile.
+template <int BN, int MH, class T>
+int launch_bn(t2sc_ctx* ctx, const CUtensorMap& tm, const ConvArgs& args, i64 max_items) {
+  static const int force_u = [] { const char* e = getenv("T2SC_UNITS"); return e ? atoi(e) : 0; }();
+  if constexpr (MH == 1 && BN <= 128) {
+    const bool two = force_u ? force_u == 2 : true;
+    if (two) return launch_u<BN, MH, 2, T>(ctx, tm, args, max_items);
+  }
+  return launch_u<BN, MH, 1, T>(ctx, tm, args, max_items);
 }
 
 template <int MH, class T>

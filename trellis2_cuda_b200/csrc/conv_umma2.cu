@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) k_conv_umma2(const __grid_consta
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, NUM_PROD_THREADS + 1 + (leader ? 1 : 0)); mbar_init(bar_empty + 8 * s, 1); mbar_init(bar_pfull + 8 * s, 1); }
     for (int b = 0; b < 2; b++) { mbar_init(bar_accf + 8 * b, 1); mbar_init(bar_acce + 8 * b, 256); }   // both CTAs' epilogue threads
-    for (int r = 0; r < IDX_SLOTS; r++) { mbar_init(bar_iready + 8 * r, 32); mbar_init(bar_ifree + 8 * r, NUM_PROD_THREADS); }
+    for (int r = 0; r < IDX_SLOTS; r++) { mbar_init(bar_iready + 8 * r, 1); mbar_init(bar_ifree + 8 * r, NUM_PROD_THREADS / 32); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -118,7 +118,8 @@ __global__ void __launch_bounds__(P_THREADS, 1) k_conv_umma2(const __grid_consta
         uint32_t idx[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) idx[i] = ring[slot * TILE_M + jbase + 16 * i];
-        mbar_arrive(bar_ifree + 8 * slot);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_ifree + 8 * slot);       // one arrival per gather warp: arrivals on one barrier serialise
         for (int c = 0; c < nchunk; c++, it++) {
           const uint32_t s = it % S, ph = (it / S) & 1;
           { long long t0 = clock64(); mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, a.status, 1); if (prof) w_empty += clock64() - t0; }
@@ -182,7 +183,8 @@ __global__ void __launch_bounds__(P_THREADS, 1) k_conv_umma2(const __grid_consta
         mbar_wait(bar_ifree + 8 * slot, iph ^ 1, abort_flag, a.status, 64);
 #pragma unroll
         for (int i = 0; i < 4; i++) ring[slot * TILE_M + lane + 32 * i] = val[i];
-        mbar_arrive(bar_iready + 8 * slot);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_iready + 8 * slot);
       }
     }
   } else if (warp == P_WARP_RELAY) {

@@ -2,9 +2,10 @@
 // per-block tap lists, 2x subdivision maps, row gather and the up-block skip add.
 //
 // Results are defined by the reference (src/spconv.cu:13-75, src/sdec.cu:21-57 of trellis2-cuda) and are
-// bit-exact with it; the layout of the work is not.  The table packs key and value into one 16-byte
-// slot so a probe is a single 128-bit load, the neighbour kernel maps one thread to one (row, tap) entry
-// so the 108-byte rows of nbr are written fully coalesced, and nothing is built on the host.
+// bit-exact with it; the layout of the work is not.  The pool-backed builders hash 2x2x2 BRICKS of voxels
+// (8 probes per row instead of 27, k_brick_*); the allocation-free builder keeps the per-voxel table with one
+// 16-byte {key, row} slot per probe and one thread per (row, tap) entry (k_hash_insert / k_neighbors).
+// Nothing is built on the host.
 #include "common.cuh"
 #include <cub/cub.cuh>
 
@@ -68,6 +69,83 @@ __global__ void __launch_bounds__(NB_THREADS) k_neighbors(const int4* __restrict
     for (int v = 1; v < 27; v++) b ^= g >> v;       // gray -> binary, src/spconv.cu:34
     gray[row0 + threadIdx.x] = (int)g;
     if (bin) bin[row0 + threadIdx.x] = (int)b;
+  }
+}
+
+// ---- brick table: one slot per occupied 2x2x2 block of voxels, holding the 8 row indices of its cells.
+// The 27 neighbours of a voxel always lie in exactly 8 bricks (2 per axis), so a row costs 8 key probes and 8
+// 32-byte value reads instead of 27 probes; the value reads of one row are shared by up to 8 taps each.
+struct __align__(16) BrickVals { uint32_t v[8]; };
+
+__device__ __forceinline__ unsigned long long brick_key(int b, int bx, int by, int bz, int Wb, int Hb, int Db) {
+  return (((unsigned long long)b * Wb + bx) * Hb + by) * Db + bz;
+}
+
+__global__ void k_brick_insert(const int4* __restrict__ coords, int n, int Wb, int Hb, int Db, unsigned long long* keys,
+                               BrickVals* vals, uint32_t mask) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int4 q = coords[i];
+  unsigned long long k = brick_key(q.x, q.y >> 1, q.z >> 1, q.w >> 1, Wb, Hb, Db);
+  int sub = (q.y & 1) | ((q.z & 1) << 1) | ((q.w & 1) << 2);
+  for (uint32_t s = mix32(k) & mask, it = 0; it <= mask; s = (s + 1) & mask, ++it) {
+    unsigned long long prev = atomicCAS(&keys[s], KEY_EMPTY, k);
+    if (prev == KEY_EMPTY || prev == k) { atomicMin(&vals[s].v[sub], (uint32_t)i); return; }   // duplicates: lowest row wins
+  }
+}
+
+// 8 threads per row, one per brick of the row's 3x3x3 neighbourhood; 32 rows per 256-thread CTA.
+__global__ void __launch_bounds__(256) k_brick_neighbors(const int4* __restrict__ coords, int n, int W, int H, int D, int Wb, int Hb, int Db,
+                                                         const unsigned long long* __restrict__ keys, const BrickVals* __restrict__ vals,
+                                                         uint32_t mask, uint32_t* __restrict__ nbr, int* __restrict__ gray, int* __restrict__ bin) {
+  const i64 row = (i64)blockIdx.x * 32 + (threadIdx.x >> 3);
+  const int t = threadIdx.x & 7;                    // brick (sx, sy, sz) = bits 0, 1, 2 of t
+  const bool live = row < n;
+  uint32_t g = 0;
+  if (live) {
+    const int4 q = coords[row];
+    const int x = q.y, y = q.z, z = q.w;
+    // along one axis the offsets -1, 0, +1 fall into brick "lo" = (c-1)>>1 or "hi" = lo + 1: odd c -> {lo, lo, hi}, even c -> {lo, hi, hi}
+    const int sx = t & 1, sy = (t >> 1) & 1, sz = t >> 2;
+    const int bx = ((x - 1) >> 1) + sx, by = ((y - 1) >> 1) + sy, bz = ((z - 1) >> 1) + sz;
+    BrickVals bv;
+#pragma unroll
+    for (int e = 0; e < 8; e++) bv.v[e] = NBR_EMPTY;
+    if (bx >= 0 && by >= 0 && bz >= 0 && bx < Wb && by < Hb && bz < Db) {
+      const unsigned long long k = brick_key(q.x, bx, by, bz, Wb, Hb, Db);
+      for (uint32_t s = mix32(k) & mask, it = 0; it <= mask; s = (s + 1) & mask, ++it) {
+        const unsigned long long sk = __ldg(keys + s);
+        if (sk == KEY_EMPTY) break;
+        if (sk == k) {
+          const uint4 a = __ldg(reinterpret_cast<const uint4*>(vals + s)), b = __ldg(reinterpret_cast<const uint4*>(vals + s) + 1);
+          bv.v[0] = a.x; bv.v[1] = a.y; bv.v[2] = a.z; bv.v[3] = a.w; bv.v[4] = b.x; bv.v[5] = b.y; bv.v[6] = b.z; bv.v[7] = b.w;
+          break;
+        }
+      }
+    }
+    // offsets of this thread's brick along each axis: first offset d0 and count
+    const int x0 = sx ? ((x & 1) ? 1 : 0) : -1, xn = sx ? ((x & 1) ? 1 : 2) : ((x & 1) ? 2 : 1);
+    const int y0 = sy ? ((y & 1) ? 1 : 0) : -1, yn = sy ? ((y & 1) ? 1 : 2) : ((y & 1) ? 2 : 1);
+    const int z0 = sz ? ((z & 1) ? 1 : 0) : -1, zn = sz ? ((z & 1) ? 1 : 2) : ((z & 1) ? 2 : 1);
+    for (int ix = 0; ix < xn; ix++)
+      for (int iy = 0; iy < yn; iy++)
+        for (int iz = 0; iz < zn; iz++) {
+          const int dx = x0 + ix, dy = y0 + iy, dz = z0 + iz;
+          const int cx = x + dx, cy = y + dy, cz = z + dz;
+          const int v = (dx + 1) * 9 + (dy + 1) * 3 + (dz + 1);                         // src/spconv.cu:27
+          uint32_t r = NBR_EMPTY;
+          if (cx >= 0 && cx < W && cy >= 0 && cy < H && cz >= 0 && cz < D) r = bv.v[(cx & 1) | ((cy & 1) << 1) | ((cz & 1) << 2)];
+          nbr[row * 27 + v] = r;
+          if (r != NBR_EMPTY) g |= 1u << v;
+        }
+  }
+  g |= __shfl_xor_sync(0xffffffffu, g, 1); g |= __shfl_xor_sync(0xffffffffu, g, 2); g |= __shfl_xor_sync(0xffffffffu, g, 4);
+  if (live && t == 0) {
+    uint32_t b = g;
+#pragma unroll
+    for (int v = 1; v < 27; v++) b ^= g >> v;       // gray -> binary, src/spconv.cu:34
+    gray[row] = (int)g;
+    if (bin) bin[row] = (int)b;
   }
 }
 
@@ -146,15 +224,19 @@ extern "C" int t2sc_build_neighbors(t2sc_ctx* ctx, const int32_t* coords, int64_
   T2_REQ(ctx, W > 0 && H > 0 && D > 0, "grid extent %d %d %d", W, H, D);
   T2_CUDA(ctx, cudaSetDevice(ctx->device));
   uint32_t cap = 1; while (cap < 2u * (uint32_t)n) cap <<= 1;            // src/spconv.cu:40
-  Slot* table = nullptr; int* bin = nullptr;
-  T2_CUDA(ctx, t2_alloc(ctx, &table, cap));
-  T2_CUDA(ctx, cudaMemsetAsync(table, 0xff, (size_t)cap * sizeof(Slot), ctx->stream));
-  k_hash_insert<<<cdiv_i(n, 256), 256, 0, ctx->stream>>>((const int4*)coords, (int)n, W, H, D, table, cap - 1);
+  int* bin = nullptr;
+  unsigned long long* bkeys = nullptr; BrickVals* bvals = nullptr;
+  const int Wb = (W + 1) / 2, Hb = (H + 1) / 2, Db = (D + 1) / 2;
+  T2_CUDA(ctx, t2_alloc(ctx, &bkeys, cap));
+  T2_CUDA(ctx, t2_alloc(ctx, &bvals, cap));
+  T2_CUDA(ctx, cudaMemsetAsync(bkeys, 0xff, (size_t)cap * sizeof(unsigned long long), ctx->stream));
+  T2_CUDA(ctx, cudaMemsetAsync(bvals, 0xff, (size_t)cap * sizeof(BrickVals), ctx->stream));
+  k_brick_insert<<<cdiv_i(n, 256), 256, 0, ctx->stream>>>((const int4*)coords, (int)n, Wb, Hb, Db, bkeys, bvals, cap - 1);
   T2_LAUNCHED(ctx);
   if (sorted) T2_CUDA(ctx, t2_alloc(ctx, &bin, (size_t)n));
-  k_neighbors<<<cdiv_i(n, NB_ROWS), NB_THREADS, 0, ctx->stream>>>((const int4*)coords, (int)n, W, H, D, table, cap - 1, nbr, gray, bin);
+  k_brick_neighbors<<<cdiv_i(n, 32), 256, 0, ctx->stream>>>((const int4*)coords, (int)n, W, H, D, Wb, Hb, Db, bkeys, bvals, cap - 1, nbr, gray, bin);
   T2_LAUNCHED(ctx);
-  t2_free(ctx, table);
+  t2_free(ctx, bkeys); t2_free(ctx, bvals);
   if (sorted) {
     int *bs = nullptr, *iota = nullptr; void* tmp = nullptr; size_t tb = 0;
     T2_CUDA(ctx, t2_alloc(ctx, &bs, (size_t)n));
@@ -291,15 +373,18 @@ extern "C" int t2sc_build_neighbors_range(t2sc_ctx* ctx, const int32_t* coords, 
   T2_REQ(ctx, W > 0 && H > 0 && D > 0, "grid extent %d %d %d", W, H, D);
   T2_CUDA(ctx, cudaSetDevice(ctx->device));
   uint32_t cap = 1; while (cap < 2u * (uint32_t)n) cap <<= 1;
-  Slot* table = nullptr;
-  T2_CUDA(ctx, t2_alloc(ctx, &table, cap));
-  T2_CUDA(ctx, cudaMemsetAsync(table, 0xff, (size_t)cap * sizeof(Slot), ctx->stream));
-  k_hash_insert<<<cdiv_i(n, 256), 256, 0, ctx->stream>>>((const int4*)coords, (int)n, W, H, D, table, cap - 1);
+  unsigned long long* bkeys = nullptr; BrickVals* bvals = nullptr;
+  const int Wb = (W + 1) / 2, Hb = (H + 1) / 2, Db = (D + 1) / 2;
+  T2_CUDA(ctx, t2_alloc(ctx, &bkeys, cap));
+  T2_CUDA(ctx, t2_alloc(ctx, &bvals, cap));
+  T2_CUDA(ctx, cudaMemsetAsync(bkeys, 0xff, (size_t)cap * sizeof(unsigned long long), ctx->stream));
+  T2_CUDA(ctx, cudaMemsetAsync(bvals, 0xff, (size_t)cap * sizeof(BrickVals), ctx->stream));
+  k_brick_insert<<<cdiv_i(n, 256), 256, 0, ctx->stream>>>((const int4*)coords, (int)n, Wb, Hb, Db, bkeys, bvals, cap - 1);
   T2_LAUNCHED(ctx);
   const i64 m = row_hi - row_lo;
-  k_neighbors<<<cdiv_i(m, NB_ROWS), NB_THREADS, 0, ctx->stream>>>((const int4*)coords + row_lo, (int)m, W, H, D, table, cap - 1, nbr, gray, nullptr);
+  k_brick_neighbors<<<cdiv_i(m, 32), 256, 0, ctx->stream>>>((const int4*)coords + row_lo, (int)m, W, H, D, Wb, Hb, Db, bkeys, bvals, cap - 1, nbr, gray, nullptr);
   T2_LAUNCHED(ctx);
-  t2_free(ctx, table);
+  t2_free(ctx, bkeys); t2_free(ctx, bvals);
   return T2SC_OK;
 }
 

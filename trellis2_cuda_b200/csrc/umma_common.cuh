@@ -27,8 +27,8 @@ constexpr int SMEM_BUDGET = 227 * 1024;
 __host__ __device__ constexpr int num_threads(int MH) { return (7 + 4 * MH) * 32; }
 __host__ __device__ constexpr int stage_bytes(int BN, int MH) { return MH * A_BYTES + BN * 128; }
 __host__ __device__ constexpr int aux_bytes(int MH) { return IDX_SLOTS * MH * TILE_M * 4 + 512; }
-__host__ __device__ constexpr int num_stages(int BN, int MH) {
-  int s = (SMEM_BUDGET - 1024 - aux_bytes(MH)) / stage_bytes(BN, MH);
+__host__ __device__ constexpr int num_stages(int BN, int MH, int U = 1) {
+  int s = (SMEM_BUDGET - 1024 - aux_bytes(MH)) / (U * stage_bytes(BN, MH));
   return s > 8 ? 8 : s;
 }
 __host__ __device__ constexpr int num_acc_bufs(int BN, int MH) { return 2 * MH * BN <= 512 ? 2 : 1; }
@@ -54,8 +54,13 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 }
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
+#ifdef T2SC_TEST_WAIT
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+#else
   asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+#endif
   return ok != 0;
 }
 // Bounded wait.  After any wait in the CTA has given up, all later waits return at once.
