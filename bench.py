@@ -139,7 +139,8 @@ def run_reference(args, rank, world):
     import oracle
     wl = make_workload(args.workload if args.workload != "cfg5" else "cfg2", 0)
     threads = os.cpu_count() or 1
-    rows = 16384 if wl["Ci"] >= 256 else 65536
+    # a bounded sample per step (about 0.15 s on 16 cores) so that any --steps the caller passes ends within minutes
+    rows = 4096 if wl["Ci"] >= 256 else 32768
     times, res = [], None
     for i in range(args.warmup + args.steps):
         res = cpu_sample(wl, rows, threads)
