@@ -25,6 +25,7 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # peer arrays are read with plain loads; no multicast object is bound
 if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":      # keeps NCCL's banner off stdout: rank 0 prints one JSON line
     os.environ["NCCL_DEBUG"] = "WARN"
 
@@ -290,6 +291,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg5"])
     ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--halo", default="p2p", choices=["p2p", "nccl"], help="cfg5: halo rows by peer-memory loads inside the conv, or by NCCL all-to-all")
     ap.add_argument("--profile", action="store_true", help="timed steps only (no end-to-end leg, no CPU baseline): for runs under ncu")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -418,6 +418,33 @@ def test_decoder_like_stack_layer_by_layer(sp):
     cache.ctx.device_status()
 
 
+def test_peer_memory_conv_reproduces_the_single_gpu_conv(sp):
+    """The conv that gathers straight from its peers' arrays (map entries = owner << 29 | row), with the "peers" being
+    three separate arrays on this one GPU: every range must give the bits of the unsharded conv."""
+    from trellis2_cuda_b200 import sharding
+    c = scenes.config2_shell()[:50000]
+    n, C = c.shape[0], 128
+    cd = dev(c)
+    x = torch.randn(n, C, device="cuda").to(torch.bfloat16)
+    w = dev(scenes.kaiming_uniform_weight(C, C, 2), torch.bfloat16)
+    b = torch.randn(C, device="cuda").to(torch.bfloat16)
+    full = sp.build_neighbors(cd, want_sorted=False)
+    want = sp.subm_conv(x, w, b, full, act="silu")
+    world = 3
+    starts = sharding.partition(n, world)
+    parts = [x[starts[r]:starts[r + 1]].clone() for r in range(world)]       # one array per "rank"
+    ptrs = [p.data_ptr() for p in parts]
+    for r in range(world):
+        lo, hi = starts[r], starts[r + 1]
+        nbr_g, gray = sp.build_neighbors_range(cd, lo, hi)
+        enc = sharding.peer_map(nbr_g, starts)
+        assert int(((enc != -1) & ((enc.to(torch.int64) & 0xFFFFFFFF) >> 29 != r)).sum()) > 0      # some rows do come from peers
+        cache = sp.cache_from_map(cd[lo:hi], enc.contiguous(), gray)
+        y = sp.subm_conv_peers(ptrs, torch.bfloat16, C, w, b, cache, act="silu")
+        assert torch.equal(y, want[lo:hi])
+    full.ctx.device_status()
+
+
 # ------------------------------------------------------------------------------------------ full-size properties
 def test_config2_properties_at_full_size(sp):
     """Configuration 2 (217,821 voxels, 256 -> 256, bf16): sampled rows against the oracle, plus

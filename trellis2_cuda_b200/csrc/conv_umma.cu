@@ -106,7 +106,9 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
 #pragma unroll
             for (int i = 0; i < 8 * MH; i++) {
               const bool present = idx[i] != NBR_EMPTY;
-              cp_async16(dst + i * (16 * 128), present ? (const void*)(xs + (i64)idx[i] * a.Ci) : (const void*)x, present ? 16u : 0u);
+              const T* base = xs; uint32_t row = idx[i];
+              if (a.npeers && present) { base = (const T*)a.xp[row >> 29] + c * KCH + c16 * 8; row &= 0x1FFFFFFFu; }   // a peer's array (P2P load)
+              cp_async16(dst + i * (16 * 128), present ? (const void*)(base + (i64)row * a.Ci) : (const void*)x, present ? 16u : 0u);
             }
           }
           if (++q == U) { cp_async_arrive_noinc(bar_full + 8 * st); q = 0; it++; }   // this thread's arrival, delivered when its copies have landed
@@ -350,7 +352,7 @@ bool conv_umma_supported(int dtype, int Ci, int Co, const EpiDev& ep) {
 }
 
 int conv_umma_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const void* w, i64 w_rows, const EpiDev& ep, void* y,
-                     int dtype, i64 n_in, int Ci, int Co) {
+                     int dtype, i64 n_in, int Ci, int Co, const void* const* x_peers, int n_peers) {
   T2_CUDA(ctx, cudaSetDevice(ctx->device));
   const int BN = pick_bn(Co);
   T2_REQ(ctx, BN > 0, "Co=%d", Co);
@@ -371,6 +373,8 @@ int conv_umma_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const 
   (void)n_in;
   static const int dbg_skip = [] { const char* e = getenv("T2SC_DEBUG_SKIP"); return e ? atoi(e) : 0; }();
   args.dbg_skip = dbg_skip;
+  args.npeers = n_peers;
+  for (int r = 0; r < 8; r++) args.xp[r] = r < n_peers ? x_peers[r] : nullptr;
   args.x = x; args.y = y; args.nbr = plan->nbr; args.order = plan->order; args.src = plan->src;
   args.tiles = plan->tiles; args.ntiles = plan->ntiles; args.status = ctx->status;
   args.Ci = Ci; args.Co = Co; args.n_cot = Co / BN; args.is_bf16 = dtype == T2SC_BF16; args.ep = ep;

@@ -322,7 +322,7 @@ int conv_umma2_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const
   ConvArgs args;
   args.x = x; args.y = y; args.nbr = plan->nbr; args.order = plan->order; args.src = plan->src;
   args.tiles = plan->tiles; args.ntiles = plan->ntiles; args.status = ctx->status;
-  args.Ci = Ci; args.Co = Co; args.n_cot = Co / P_BN; args.is_bf16 = dtype == T2SC_BF16; args.ep = ep;
+  args.Ci = Ci; args.Co = Co; args.n_cot = Co / P_BN; args.is_bf16 = dtype == T2SC_BF16; args.ep = ep; args.npeers = 0;
   static const int dbg_skip = [] { const char* e = getenv("T2SC_DEBUG_SKIP"); return e ? atoi(e) : 0; }();
   args.dbg_skip = dbg_skip;
   const i64 max_items = plan->max_tiles * args.n_cot;

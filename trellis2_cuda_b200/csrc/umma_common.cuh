@@ -37,6 +37,8 @@ struct ConvArgs {
   const void* x; void* y; const uint32_t* nbr; const int* order; const int* src;
   const PlanTile* tiles; const int* ntiles; int* status;
   int Ci, Co, n_cot, is_bf16;
+  int npeers;               // > 0: map entries are (owner << 29) | row and rows are read from xp[owner]
+  const void* xp[8];
   int dbg_skip;      // measurement aid (T2SC_DEBUG_SKIP): 1 = no A gather, 2 = no B load, 4 = no MMA (results are then invalid), 8 = CTA 0 prints where each role waited
   EpiDev ep;
 };

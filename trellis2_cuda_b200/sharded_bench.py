@@ -9,6 +9,7 @@ its blocks.
 from __future__ import annotations
 
 import json
+import os
 import time
 
 import numpy as np
@@ -39,19 +40,33 @@ def run(args, rank, world, local_rank, METRIC, peaks, ClockSampler, visible_gpu_
     starts = sharding.partition(N, world)
     lo, hi = starts[rank], starts[rank + 1]
 
+    p2p = args.halo == "p2p" and world > 1
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     nbr_g, gray = sp.build_neighbors_range(coords, lo, hi)
     plan = sharding.build_halo_plan(nbr_g, rank, world, starts)
+    if p2p:      # the conv gathers halo rows from the peers' arrays itself: the map names (owner, row), nothing is copied
+        cache = sp.cache_from_map(coords[lo:hi], sharding.peer_map(nbr_g, starts).contiguous(), gray)
+    else:
+        cache = sp.cache_from_map(coords[lo:hi], plan.nbr_local.contiguous(), gray)
     del nbr_g
-    cache = sp.cache_from_map(coords[lo:hi], plan.nbr_local.contiguous(), gray)
     st = cache.plan_for(C).stats()
     torch.cuda.synchronize()
     setup_ms = (time.perf_counter() - t0) * 1e3
 
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
-    xa = torch.zeros((plan.n_local, C), dtype=td, device=dev)
-    xb = torch.zeros((plan.n_local, C), dtype=td, device=dev)
+    if p2p:
+        import torch.distributed._symmetric_memory as symm
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")      # plain peer loads only
+        rows_max = max(starts[r + 1] - starts[r] for r in range(world))
+        xa = symm.empty((rows_max, C), dtype=td, device=dev)
+        xb = symm.empty((rows_max, C), dtype=td, device=dev)
+        ha, hb = symm.rendezvous(xa, dist.group.WORLD), symm.rendezvous(xb, dist.group.WORLD)
+        ptrs = {xa.data_ptr(): [int(p) for p in ha.buffer_ptrs], xb.data_ptr(): [int(p) for p in hb.buffer_ptrs]}
+        hdl = {xa.data_ptr(): ha, xb.data_ptr(): hb}
+    else:
+        xa = torch.zeros((plan.n_local, C), dtype=td, device=dev)
+        xb = torch.zeros((plan.n_local, C), dtype=td, device=dev)
     x0 = torch.randn((plan.n_own, C), generator=g, device=dev).to(td)
     ws = [torch.from_numpy(scenes.kaiming_uniform_weight(C, C, 100 + l)).to(dev).to(td) for l in range(layers)]
     pack = lambda x_own, idx: sp.gather_rows(x_own, idx, C)
@@ -62,11 +77,19 @@ def run(args, rank, world, local_rank, METRIC, peaks, ClockSampler, visible_gpu_
         for l in range(layers):
             if timers:
                 timers[0][l].record()
-            sharding.exchange_halo(plan, a, pack)
+            if p2p:
+                hdl[a.data_ptr()].barrier(channel=l % 2)       # every rank has written the array this layer reads
+            else:
+                sharding.exchange_halo(plan, a, pack)
             if timers:
                 timers[1][l].record()
-            sp.subm_conv_local(a, ws[l], None, cache, out=b[:plan.n_own])
+            if p2p:
+                sp.subm_conv_peers(ptrs[a.data_ptr()], td, C, ws[l], None, cache, out=b[:plan.n_own])
+            else:
+                sp.subm_conv_local(a, ws[l], None, cache, out=b[:plan.n_own])
             a, b = b, a
+        if p2p:
+            hdl[a.data_ptr()].barrier(channel=0)               # nobody overwrites an array a peer may still be reading
         return a
 
     for _ in range(args.warmup):
@@ -131,7 +154,7 @@ def run(args, rank, world, local_rank, METRIC, peaks, ClockSampler, visible_gpu_
     line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"cfg5: 2048^3 shell of 12 spheres/tori, {layers} stacked 128->128 submanifold convs, equal-count Morton ranges, "
-                                   "one-voxel halo by NCCL all-to-all per layer", "voxels": N, "Cin": C, "Cout": C, "active_taps": int(T_all),
+                                   + ("halo rows read from peer memory by the conv kernel (P2P), one device barrier per layer" if p2p else "one-voxel halo by NCCL all-to-all per layer"), "voxels": N, "Cin": C, "Cout": C, "active_taps": int(T_all),
                        "computed_taps": int(sums[2].item()), "halo_rows_total": int(sums[1].item()), "step": f"{layers} x (halo exchange + conv)",
                        "l2": "inputs larger than L2 (per-rank features >= 275 MB)"},
             "voxels_per_s": N * layers / (ms * 1e-3), "exchange_ms_per_step": vals[1].item() / args.steps, "setup_ms": vals[3].item(),

@@ -62,6 +62,24 @@ def local_map(nbr_global: torch.Tensor, lo: int, hi: int, starts: List[int]):
     return halo, nbr_local, recv_counts
 
 
+PEER_SHIFT = 29        # map entries of the peer-memory conv: (owner rank << 29) | row inside the owner's array
+
+
+def peer_map(nbr_global: torch.Tensor, starts: List[int]) -> torch.Tensor:
+    """No communication and no halo copies: rewrites an owned-rows neighbour map with global indices into the form the
+    peer-memory conv reads, (owner << 29) | (global row - first row of the owner); absent stays -1 (0xffffffff)."""
+    world = len(starts) - 1
+    if world > 8 or max(starts[r + 1] - starts[r] for r in range(world)) >= (1 << PEER_SHIFT):
+        raise ValueError("peer maps hold at most 8 ranks and 2^29 rows per rank")
+    g = nbr_global.to(torch.int64)
+    present = g >= 0
+    bounds = torch.tensor(starts, dtype=torch.int64, device=g.device)
+    owner = (torch.searchsorted(bounds, g.clamp(min=0), right=True) - 1).clamp(max=world - 1)
+    enc = (owner << PEER_SHIFT) | (g - bounds[owner])
+    enc = torch.where(present, enc, torch.full_like(enc, 0xFFFFFFFF))
+    return (enc & 0xFFFFFFFF).to(torch.int64).where(enc < (1 << 31), enc - (1 << 32)).to(torch.int32)     # same bits in int32 storage
+
+
 def build_halo_plan(nbr_global: torch.Tensor, rank: int, world: int, starts: List[int], group=None) -> HaloPlan:
     """From the owned rows' neighbour map (global indices) derive the halo, the local map and, by exchanging the
     wanted-row lists, what to send to whom.  Collective over `group`."""
