@@ -33,7 +33,7 @@ using namespace umma;
 // 7.. epilogue (4 warps per 128-row half).
 // U = (tap, 64-channel chunk) units per pipeline stage: 1, or 2 for narrow layers, where one unit is too little work
 // for the cost of a barrier round trip.
-template <int BN, int MH, int U, class T>
+template <int BN, int MH, int U, bool PEERS, class T>
 __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_constant__ CUtensorMap tmw, const ConvArgs a) {
   constexpr int UNIT = stage_bytes(BN, MH);          // one unit: MH gathered A halves + one weight slab
   constexpr int STAGE = U * UNIT;
@@ -49,6 +49,7 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
   uint64_t* bars = (uint64_t*)(ring + IDX_SLOTS * ROWS);   // full[S] empty[S] accf[2] acce[2] iready[IDX_SLOTS] ifree[IDX_SLOTS]
   uint32_t* tmem_slot = (uint32_t*)(bars + 2 * S + 4 + 2 * IDX_SLOTS);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  const void** peer_base = (const void**)(tmem_slot + 2);      // the peers' array addresses (PEERS only)
 
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * S, bar_accf = bar_empty + 8 * S, bar_acce = bar_accf + 16,
@@ -60,6 +61,7 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
     for (int b = 0; b < 2; b++) { mbar_init(bar_accf + 8 * b, 1); mbar_init(bar_acce + 8 * b, 128 * MH); }
     for (int r = 0; r < IDX_SLOTS; r++) { mbar_init(bar_iready + 8 * r, 1); mbar_init(bar_ifree + 8 * r, NUM_PROD_THREADS / 32); }
     *abort_flag = 0;
+    if (PEERS) for (int r = 0; r < 8; r++) peer_base[r] = a.xp[r];
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -106,9 +108,12 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
 #pragma unroll
             for (int i = 0; i < 8 * MH; i++) {
               const bool present = idx[i] != NBR_EMPTY;
-              const T* base = xs; uint32_t row = idx[i];
-              if (a.npeers && present) { base = (const T*)a.xp[row >> 29] + c * KCH + c16 * 8; row &= 0x1FFFFFFFu; }   // a peer's array (P2P load)
-              cp_async16(dst + i * (16 * 128), present ? (const void*)(base + (i64)row * a.Ci) : (const void*)x, present ? 16u : 0u);
+              if constexpr (PEERS) {      // entry = (owner << 29) | row: read the row from the owner's array (a P2P load for a peer)
+                const T* base = (const T*)peer_base[idx[i] >> 29] + c * KCH + c16 * 8;
+                cp_async16(dst + i * (16 * 128), present ? (const void*)(base + (i64)(idx[i] & 0x1FFFFFFFu) * a.Ci) : (const void*)x, present ? 16u : 0u);
+              } else {
+                cp_async16(dst + i * (16 * 128), present ? (const void*)(xs + (i64)idx[i] * a.Ci) : (const void*)x, present ? 16u : 0u);
+              }
             }
           }
           if (++q == U) { cp_async_arrive_noinc(bar_full + 8 * st); q = 0; it++; }   // this thread's arrival, delivered when its copies have landed
@@ -303,30 +308,31 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-template <int BN, int MH, int U, class T>
-int launch_u(t2sc_ctx* ctx, const CUtensorMap& tm, const ConvArgs& args, i64 max_items) {
+template <int BN, int MH, int U, bool PEERS, class T>
+int launch_p(t2sc_ctx* ctx, const CUtensorMap& tm, const ConvArgs& args, i64 max_items) {
   constexpr int smem = num_stages(BN, MH, U) * U * stage_bytes(BN, MH) + aux_bytes(MH) + 1024;
   static_assert(smem <= SMEM_BUDGET && num_stages(BN, MH, U) >= 3, "shared memory budget");
   static bool attr_set[16] = {};
   if (!attr_set[ctx->device & 15]) {
-    T2_CUDA(ctx, cudaFuncSetAttribute(k_conv_umma<BN, MH, U, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    T2_CUDA(ctx, cudaFuncSetAttribute(k_conv_umma<BN, MH, U, PEERS, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set[ctx->device & 15] = true;
   }
   int grid = (int)(max_items < ctx->num_sms ? max_items : ctx->num_sms);
-  k_conv_umma<BN, MH, U, T><<<grid, num_threads(MH), smem, ctx->stream>>>(tm, args);
+  k_conv_umma<BN, MH, U, PEERS, T><<<grid, num_threads(MH), smem, ctx->stream>>>(tm, args);
   T2_LAUNCHED(ctx);
   return T2SC_OK;
 }
 
-// Two units per stage where a unit is small: 128-row tiles with at most 128 output channels per tile.
+// One (tap, chunk) unit per stage by default; T2SC_UNITS=2 selects two (measured: no gain, kept for experiments).
+// The peer-memory form exists for 128-row and 256-row tiles with one unit per stage.
 template <int BN, int MH, class T>
 int launch_bn(t2sc_ctx* ctx, const CUtensorMap& tm, const ConvArgs& args, i64 max_items) {
   static const int force_u = [] { const char* e = getenv("T2SC_UNITS"); return e ? atoi(e) : 0; }();
+  if (args.npeers > 0) return launch_p<BN, MH, 1, true, T>(ctx, tm, args, max_items);
   if constexpr (MH == 1 && BN <= 128) {
-    const bool two = force_u ? force_u == 2 : true;
-    if (two) return launch_u<BN, MH, 2, T>(ctx, tm, args, max_items);
+    if (force_u == 2) return launch_p<BN, MH, 2, false, T>(ctx, tm, args, max_items);
   }
-  return launch_u<BN, MH, 1, T>(ctx, tm, args, max_items);
+  return launch_p<BN, MH, 1, false, T>(ctx, tm, args, max_items);
 }
 
 template <int MH, class T>
