@@ -95,6 +95,14 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
         uint32_t idx[8 * MH];       // rows jbase + 16 i; rows 128.. are the second half, stored right behind the first
 #pragma unroll
         for (int i = 0; i < 8 * MH; i++) idx[i] = ring[slot * ROWS + jbase + 16 * i];
+        // PEERS: entry = (owner << 29) | row.  The row addresses are formed here, once per tap: a table load between the
+        // copies below would be ordered after each of them and serialise the loop.
+        const T* rp[PEERS ? 8 * MH : 1];
+        if constexpr (PEERS) {
+#pragma unroll
+          for (int i = 0; i < 8 * MH; i++)
+            rp[i] = idx[i] != NBR_EMPTY ? (const T*)peer_base[idx[i] >> 29] + (i64)(idx[i] & 0x1FFFFFFFu) * a.Ci + c16 * 8 : nullptr;
+        }
         __syncwarp();
         if (lane == 0 && !noring) mbar_arrive(bar_ifree + 8 * slot);       // one arrival per gather warp: arrivals on one barrier serialise
         for (int c = 0; c < nchunk; c++) {
@@ -107,11 +115,10 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
           if (!(a.dbg_skip & 1)) {
 #pragma unroll
             for (int i = 0; i < 8 * MH; i++) {
-              const bool present = idx[i] != NBR_EMPTY;
-              if constexpr (PEERS) {      // entry = (owner << 29) | row: read the row from the owner's array (a P2P load for a peer)
-                const T* base = (const T*)peer_base[idx[i] >> 29] + c * KCH + c16 * 8;
-                cp_async16(dst + i * (16 * 128), present ? (const void*)(base + (i64)(idx[i] & 0x1FFFFFFFu) * a.Ci) : (const void*)x, present ? 16u : 0u);
+              if constexpr (PEERS) {      // a P2P load when the owner is a peer
+                cp_async16(dst + i * (16 * 128), rp[i] ? (const void*)(rp[i] + c * KCH) : (const void*)x, rp[i] ? 16u : 0u);
               } else {
+                const bool present = idx[i] != NBR_EMPTY;
                 cp_async16(dst + i * (16 * 128), present ? (const void*)(xs + (i64)idx[i] * a.Ci) : (const void*)x, present ? 16u : 0u);
               }
             }
