@@ -57,9 +57,10 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, NUM_PROD_THREADS + 1); mbar_init(bar_empty + 8 * s, 1); }
+    const int ngw = (a.dbg_skip & 2048) ? 1 : NUM_PROD_THREADS / 32;       // measurement aid: one gather warp only
+    for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, ngw * 32 + ((a.dbg_skip & 512) ? 0 : 1)); mbar_init(bar_empty + 8 * s, 1); }
     for (int b = 0; b < 2; b++) { mbar_init(bar_accf + 8 * b, 1); mbar_init(bar_acce + 8 * b, 128 * MH); }
-    for (int r = 0; r < IDX_SLOTS; r++) { mbar_init(bar_iready + 8 * r, 1); mbar_init(bar_ifree + 8 * r, NUM_PROD_THREADS / 32); }
+    for (int r = 0; r < IDX_SLOTS; r++) { mbar_init(bar_iready + 8 * r, 1); mbar_init(bar_ifree + 8 * r, ngw); }
     *abort_flag = 0;
     if (PEERS) for (int r = 0; r < 8; r++) peer_base[r] = a.xp[r];
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -79,14 +80,17 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
   const int nchunk = a.Ci / KCH;
 
   if (warp < 4) {
+    if ((a.dbg_skip & 2048) && warp > 0) goto role_done;
     // ===================================================================== A producer: gather rows into the swizzled tile
     const T* x = (const T*)a.x;
     const int t = threadIdx.x, jbase = t >> 3, c16 = t & 7;
     const uint32_t dst_thread = (uint32_t)(jbase * 128 + ((c16 ^ (jbase & 7)) << 4));   // (jbase + 16 i) & 7 == jbase & 7
     uint32_t it = 0, iit = 0;
     const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_idx = 0, w_empty = 0, t_role = clock64();
+    PlanTile tile_next = blockIdx.x < nitems ? a.tiles[blockIdx.x / a.n_cot] : PlanTile{};
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
-      const PlanTile tile = a.tiles[item / a.n_cot];
+      const PlanTile tile = tile_next;
+      if (item + (int)gridDim.x < nitems) tile_next = a.tiles[(item + gridDim.x) / a.n_cot];     // in flight while this tile is gathered
       int q = 0; uint32_t st = 0;
       for (uint32_t mk = tile.mask; mk; mk &= mk - 1, iit++) {
         const uint32_t slot = iit % IDX_SLOTS, iph = (iit / IDX_SLOTS) & 1;
@@ -132,34 +136,36 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
     if (prof && blockIdx.x == 0 && threadIdx.x == 0)
       printf("[t2sc prof] gather: total %lld clk, wait index ring %lld, wait stage free %lld, stages %u\n", clock64() - t_role, w_idx, w_empty, it);
   } else if (warp == WARP_TMA) {
-    // ===================================================================== B producer (weights by TMA)
-    uint32_t it = 0;
-    for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
-      const int tile_id = item / a.n_cot, cot = item - tile_id * a.n_cot;
-      const PlanTile tile = a.tiles[tile_id];
-      const int wrow = tile.wbase * a.Co + cot * BN;
-      const int nunits = __popc(tile.mask) * nchunk;
-      int q = 0, u = 0; uint32_t st = 0;
-      for (uint32_t mk = tile.mask; mk; mk &= mk - 1) {
-        const int v = __ffs(mk) - 1;
-        for (int c = 0; c < nchunk; c++, u++) {
-          if (q == 0) {
-            st = it % S;
-            mbar_wait(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 2);
-            const int nq = nunits - u < U ? nunits - u : U;
-            if (lane == 0) {
+    // ===================================================================== B producer (weights by TMA): one lane does it all
+    if (lane == 0 && !(a.dbg_skip & 512)) {
+      uint32_t it = 0;
+      PlanTile tile_next = blockIdx.x < nitems ? a.tiles[blockIdx.x / a.n_cot] : PlanTile{};
+      for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+        const int tile_id = item / a.n_cot, cot = item - tile_id * a.n_cot;
+        const PlanTile tile = tile_next;
+        if (item + (int)gridDim.x < nitems) tile_next = a.tiles[(item + gridDim.x) / a.n_cot];
+        const int wrow = tile.wbase * a.Co + cot * BN;
+        const int nunits = __popc(tile.mask) * nchunk;
+        int q = 0, u = 0; uint32_t st = 0;
+        for (uint32_t mk = tile.mask; mk; mk &= mk - 1) {
+          const int v = __ffs(mk) - 1;
+          for (int c = 0; c < nchunk; c++, u++) {
+            if (q == 0) {
+              st = it % S;
+              mbar_wait(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 2);
+              const int nq = nunits - u < U ? nunits - u : U;
               if (a.dbg_skip & 2) mbar_arrive(bar_full + 8 * st);
               else mbar_arrive_expect_tx(bar_full + 8 * st, nq * B_BYTES);
             }
+            if (!(a.dbg_skip & 2))
+              tma_load_3d(smem_base + st * STAGE + q * UNIT + MH * A_BYTES, &tmw, c * KCH, v, wrow, bar_full + 8 * st);
+            if (++q == U) { q = 0; it++; }
           }
-          if (lane == 0 && !(a.dbg_skip & 2))
-            tma_load_3d(smem_base + st * STAGE + q * UNIT + MH * A_BYTES, &tmw, c * KCH, v, wrow, bar_full + 8 * st);
-          __syncwarp();
-          if (++q == U) { q = 0; it++; }
         }
+        if (q != 0) it++;
       }
-      if (q != 0) it++;
     }
+    __syncwarp();
   } else if (warp == WARP_IDX) {
     // ===================================================================== neighbour indices, one ring slot per (tile, tap)
     // Runs ahead of the gather warps across tile boundaries, so a new tile starts without a dependent-load bubble.
@@ -168,9 +174,7 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
     constexpr int NR = 4 * MH;
     uint32_t iit = 0;
     const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_free = 0, w_load = 0, t_role = clock64();
-    auto rows_of = [&](int item, int* nr) {
-      if (item >= nitems) return;
-      const PlanTile tl = a.tiles[item / a.n_cot];
+    auto rows_of = [&](const PlanTile& tl, int* nr) {
 #pragma unroll
       for (int i = 0; i < NR; i++) {
         const int j = lane + 32 * i;
@@ -202,11 +206,15 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
         iit++;
       }
     };
+    // tile descriptors are fetched two tiles ahead and row numbers one tile ahead, so no dependent load sits on a tile boundary
+    auto desc_of = [&](int item) { return item < nitems ? a.tiles[item / a.n_cot] : PlanTile{}; };
     int nr[NR], nr_next[NR];
-    rows_of(blockIdx.x, nr);
+    PlanTile tile_n0 = desc_of(blockIdx.x), tile_n1 = desc_of(blockIdx.x + gridDim.x);
+    rows_of(tile_n0, nr);
     for (int item = blockIdx.x; item < nitems && !(a.dbg_skip & 128); item += gridDim.x) {
-      const PlanTile tile = a.tiles[item / a.n_cot];
-      rows_of(item + gridDim.x, nr_next);                      // in flight while this tile is served
+      const PlanTile tile = tile_n0;
+      const PlanTile tile_n2 = desc_of(item + 2 * gridDim.x);
+      rows_of(tile_n1, nr_next);                               // in flight while this tile is served
       uint32_t mk_load = tile.mask, mk_ret = tile.mask;
       uint32_t va[IDX_ROUND][NR], vb[IDX_ROUND][NR];
       load_round(va, mk_load, nr);
@@ -219,29 +227,33 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
       }
 #pragma unroll
       for (int i = 0; i < NR; i++) nr[i] = nr_next[i];
+      tile_n0 = tile_n1; tile_n1 = tile_n2;
     }
     if (prof && blockIdx.x == 0 && lane == 0)
       printf("[t2sc prof] index warp: total %lld clk, wait slot free %lld, wait own loads %lld, slots %u\n", clock64() - t_role, w_free, w_load, iit);
   } else if (warp == WARP_MMA) {
-    // ===================================================================== MMA issuer
-    const uint32_t idesc = umma_idesc(BN, a.is_bf16);
-    uint32_t it = 0, acc_it = 0;
-    const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_full = 0, w_acc = 0, w_issue = 0, w_commit = 0, t_role = clock64();
-    for (int item = blockIdx.x; item < nitems; item += gridDim.x, acc_it++) {
-      const int tile_id = item / a.n_cot;
-      const PlanTile tile = a.tiles[tile_id];
-      const uint32_t buf = acc_it % NB, aph = (acc_it / NB) & 1;
-      mbar_wait_t(bar_acce + 8 * buf, aph ^ 1, abort_flag, a.status, 4, prof, w_acc);
-      tc_fence_after();
-      const uint32_t d_tmem = tmem_base + buf * (MH * BN);
-      const int halves = tile.rows > TILE_M ? MH : 1;
-      const int nunits = __popc(tile.mask) * nchunk;
-      for (int u0 = 0; u0 < nunits; u0 += U, it++) {
-        const uint32_t s = it % S, ph = (it / S) & 1;
-        mbar_wait_t(bar_full + 8 * s, ph, abort_flag, a.status, 8, prof, w_full);
-        tc_fence_after();
-        long long ti0 = prof ? clock64() : 0;
-        if (lane == 0) {
+    // ===================================================================== MMA issuer: one lane waits, issues and commits
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(BN, a.is_bf16);
+      uint32_t it = 0, acc_it = 0;
+      const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_full = 0, w_acc = 0, w_issue = 0, w_commit = 0, t_role = clock64();
+      PlanTile tile_next = blockIdx.x < nitems ? a.tiles[blockIdx.x / a.n_cot] : PlanTile{};
+      for (int item = blockIdx.x; item < nitems; item += gridDim.x, acc_it++) {
+        const PlanTile tile = tile_next;
+        if (item + (int)gridDim.x < nitems) tile_next = a.tiles[(item + gridDim.x) / a.n_cot];
+        const uint32_t buf = acc_it % NB, aph = (acc_it / NB) & 1;
+        if (!(a.dbg_skip & 1024)) mbar_wait_t(bar_acce + 8 * buf, aph ^ 1, abort_flag, a.status, 4, prof, w_acc);
+        tc_fence_after();                       // the epilogue's tcgen05.ld of this buffer come before the MMAs that overwrite it
+        const uint32_t d_tmem = tmem_base + buf * (MH * BN);
+        const int halves = tile.rows > TILE_M ? MH : 1;
+        const int nunits = __popc(tile.mask) * nchunk;
+        for (int u0 = 0; u0 < nunits; u0 += U, it++) {
+          const uint32_t s = it % S, ph = (it / S) & 1;
+          // No tcgen05 fence after this wait (the operands are shared-memory data published by the barrier, not tcgen05
+          // results) and no proxy fence either: the copies' completion is delivered through the barrier itself
+          // (cp.async.mbarrier.arrive.noinc); a fence.proxy.async here was measured at 3-12 % of the kernel time.
+          mbar_wait_t(bar_full + 8 * s, ph, abort_flag, a.status, 8, prof, w_full);
+          long long ti0 = prof ? clock64() : 0;
           const int nq = nunits - u0 < U ? nunits - u0 : U;
           for (int q = 0; q < nq && !(a.dbg_skip & 4); q++) {
             const uint64_t bd = umma_desc(smem_base + s * STAGE + q * UNIT + MH * A_BYTES);
@@ -256,23 +268,25 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
           tc_commit(bar_empty + 8 * s);
           if (prof) { w_issue += ti1 - ti0; w_commit += clock64() - ti1; }
         }
-        __syncwarp();
+        if (!(a.dbg_skip & 1024)) tc_commit(bar_accf + 8 * buf);
       }
-      if (lane == 0) tc_commit(bar_accf + 8 * buf);
-      __syncwarp();
+      if (prof && blockIdx.x == 0)
+        printf("[t2sc prof] mma: total %lld clk, wait stage full %lld, wait accumulator free %lld, mma issue %lld, commit %lld, steps %u, tiles %u\n",
+               clock64() - t_role, w_full, w_acc, w_issue, w_commit, it, acc_it);
     }
-    if (prof && blockIdx.x == 0 && lane == 0)
-      printf("[t2sc prof] mma: total %lld clk, wait stage full %lld, wait accumulator free %lld, mma issue %lld, commit %lld, steps %u, tiles %u\n",
-             clock64() - t_role, w_full, w_acc, w_issue, w_commit, it, acc_it);
+    __syncwarp();
   } else {
     // ===================================================================== epilogue
     const bool has_skip = a.ep.skip_x != nullptr;
     const int q = warp & 3, half = (warp - WARP_EPI0) >> 2, j = half * TILE_M + q * 32 + lane;
     uint32_t acc_it = 0;
     const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_accf = 0, t_role = clock64();
+    if (a.dbg_skip & 1024) goto role_done;
+    PlanTile tile_next = blockIdx.x < nitems ? a.tiles[blockIdx.x / a.n_cot] : PlanTile{};
     for (int item = blockIdx.x; item < nitems; item += gridDim.x, acc_it++) {
       const int tile_id = item / a.n_cot, cot = item - tile_id * a.n_cot;
-      const PlanTile tile = a.tiles[tile_id];
+      const PlanTile tile = tile_next;
+      if (item + (int)gridDim.x < nitems) tile_next = a.tiles[(item + gridDim.x) / a.n_cot];
       const uint32_t buf = acc_it % NB, aph = (acc_it / NB) & 1;
       const int orow = j < tile.rows ? a.order[tile.start + j] : -1;
       const int wcol0 = tile.wbase * a.Co + cot * BN;      // bias index of this item's first column
@@ -289,6 +303,7 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
       printf("[t2sc prof] epilogue: total %lld clk, wait accumulator full %lld (busy %lld), tiles %u\n", clock64() - t_role, w_accf, clock64() - t_role - w_accf, acc_it);
   }
 
+role_done:
   tc_fence_before();
   __syncthreads();
   if (*abort_flag) {        // a wait gave up: let copies still in flight land before the smem and TMEM are released
@@ -385,7 +400,7 @@ int conv_umma_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const 
   ConvArgs args;
   (void)n_in;
   static const int dbg_skip = [] { const char* e = getenv("T2SC_DEBUG_SKIP"); return e ? atoi(e) : 0; }();
-  args.dbg_skip = dbg_skip;
+  args.dbg_skip = dbg_skip | ((dbg_skip & (128 | 512 | 1024 | 2048)) ? (1 | 2 | 4 | 32 | 64) : 0);   // handshake experiments never touch data
   args.npeers = n_peers;
   for (int r = 0; r < 8; r++) args.xp[r] = r < n_peers ? x_peers[r] : nullptr;
   args.x = x; args.y = y; args.nbr = plan->nbr; args.order = plan->order; args.src = plan->src;

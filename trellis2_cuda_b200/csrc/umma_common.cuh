@@ -29,6 +29,9 @@ __host__ __device__ constexpr int stage_bytes(int BN, int MH) { return MH * A_BY
 __host__ __device__ constexpr int aux_bytes(int MH) { return IDX_SLOTS * MH * TILE_M * 4 + 512; }
 __host__ __device__ constexpr int num_stages(int BN, int MH, int U = 1) {
   int s = (SMEM_BUDGET - 1024 - aux_bytes(MH)) / (U * stage_bytes(BN, MH));
+#ifdef T2SC_MAX_STAGES
+  if (s > T2SC_MAX_STAGES) s = T2SC_MAX_STAGES;      // measurement aid
+#endif
   return s > 8 ? 8 : s;
 }
 __host__ __device__ constexpr int num_acc_bufs(int BN, int MH) { return 2 * MH * BN <= 512 ? 2 : 1; }
@@ -56,20 +59,26 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 }
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
-#ifdef T2SC_TEST_WAIT
-  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-#else
   asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+#ifndef T2SC_WAIT_HINT_NS
+#define T2SC_WAIT_HINT_NS 2000
 #endif
+// The same with a suspend-time hint: the thread sleeps in hardware until the phase completes or the hint runs out, so a
+// long wait does not keep re-issuing polls that compete with the working warps for issue slots and the shared-memory path.
+__device__ __forceinline__ bool mbar_try_sleep(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity), "r"((uint32_t)T2SC_WAIT_HINT_NS) : "memory");
   return ok != 0;
 }
 // Bounded wait.  After any wait in the CTA has given up, all later waits return at once.
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
   if (mbar_try(bar, parity)) return;
   long long t0 = clock64();
-  while (!mbar_try(bar, parity)) {
+  while (!mbar_try_sleep(bar, parity)) {
     if (*abort_flag || clock64() - t0 > WAIT_LIMIT_CYCLES) { *abort_flag = 1; atomicOr(status, code); return; }
   }
 }
