@@ -337,6 +337,30 @@ def test_two_sm_variant_equals_single_cta_kernel(sp):
         sp.subm_conv(xd, wd, bd, sp.build_neighbors(dev(c), tile_rows=128), variant="umma_pair")
 
 
+def test_rows_without_any_neighbour(sp):
+    """A caller-supplied map may hold rows (here: whole tiles) with no neighbour at all, not even themselves.  Their
+    output is the epilogue of a zero accumulator (the bias), never uninitialised tensor memory."""
+    rng = np.random.default_rng(5)
+    n, C = 700, 64
+    c, x, w, b = conv_case(rng, n, 10, C, C, "bf16")
+    full = sp.build_neighbors(dev(c), want_sorted=False)
+    nbr, gray = full.nbr.clone(), full.gray.clone()
+    dead = torch.zeros(n, dtype=torch.bool, device="cuda")
+    dead[100:420] = True                                   # more than two whole 128-row tiles after the mask sort
+    nbr[dead] = -1
+    gray[dead] = 0
+    nbr_o = host(nbr).astype(np.int64)
+    nbr_o[nbr_o < 0] = oracle.EMPTY
+    want = oracle.conv_block(x, w, b, nbr_o.astype(np.uint32), "bf16")
+    for tile_rows in (128, 256):
+        cache = sp.cache_from_map(dev(c), nbr.contiguous(), gray.contiguous(), tile_rows=tile_rows)
+        for variant in ("umma", "simt"):
+            y = sp.subm_conv(dev(x, TD["bf16"]), dev(w, TD["bf16"]), dev(b, TD["bf16"]), cache, variant=variant)
+            cache.ctx.device_status()
+            check_feats(host(y), want, f"dead rows {variant} tile {tile_rows}")
+            assert torch.equal(y[dead], dev(b, TD["bf16"]).expand(int(dead.sum()), C))
+
+
 def test_sharded_ranks_reproduce_the_single_gpu_conv(sp):
     """Two and three Morton ranges emulated one after the other on one GPU: each range's local map (owned rows +
     appended halo rows) through the unchanged conv kernel gives the same bits as the unsharded conv."""

@@ -73,6 +73,7 @@ __global__ void k_plan_tiles(const int* __restrict__ gray, const int* __restrict
   }
   o = __reduce_or_sync(0xffffffffu, o);
   act = __reduce_add_sync(0xffffffffu, act);
+  if (o == 0) o = 1u << 13;       // no row of the tile has any neighbour: one tap of zero-filled rows still initialises the accumulators
   if (lane == 0) {
     tiles[t] = PlanTile{start, rows, g, o};      // wbase holds the group; the conv multiplies by Co
     atomicAdd(&stats[0], (unsigned long long)rows * __popc(o));
