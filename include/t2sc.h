@@ -140,13 +140,13 @@ int t2sc_subm_conv(t2sc_ctx* ctx, t2sc_plan* plan, const void* x, const void* w,
 
 /* The same operator for one rank of a Morton-range partition, reading its inputs straight from its peers' memory: the
  * gather of the conv kernel itself is the halo exchange (no pack kernel, no collective in the data path).  x_peers[r]
- * is rank r's feature array [rows_r, Ci], mapped into this process (CUDA IPC / symmetric memory; x_peers[own rank] is
- * the local array); every present entry of the plan's neighbour map is (owner rank << 29) | (row within the owner's
+ * is rank r's feature array [rows_r, Ci], mapped into this process (CUDA IPC / symmetric memory; x_peers[self_rank] is
+ * the local array: taps whose rows are all local, nearly all of them, take the ordinary gather path); every present entry of the plan's neighbour map is (owner rank << 29) | (row within the owner's
  * array), 0xffffffff = absent.  At most 8 peers, fewer than 2^29 rows per rank.  The caller orders the ranks: a layer
  * may start only when every peer has finished writing the array it reads.  Only the tcgen05 path (fp16 / bf16,
  * Ci % 64 == 0, Co % 32 == 0).  The reference is single-GPU and has no counterpart. */
-int t2sc_subm_conv_peers(t2sc_ctx* ctx, t2sc_plan* plan, const void* const* x_peers, int n_peers, const void* w,
-                         const t2sc_epilogue* ep, void* y, int dtype, int Ci, int Co);
+int t2sc_subm_conv_peers(t2sc_ctx* ctx, t2sc_plan* plan, const void* const* x_peers, int n_peers, int self_rank,
+                         const void* w, const t2sc_epilogue* ep, void* y, int dtype, int Ci, int Co);
 
 /* Replaces layer_norm + act_ + add_ (src/ops.cu:17-113) as one pass over [n,C]; any of the three may
  * be disabled (ln = 0, act = 0, residual = NULL).  In place when y == x. */

@@ -464,7 +464,7 @@ def test_peer_memory_conv_reproduces_the_single_gpu_conv(sp):
         enc = sharding.peer_map(nbr_g, starts)
         assert int(((enc != -1) & ((enc.to(torch.int64) & 0xFFFFFFFF) >> 29 != r)).sum()) > 0      # some rows do come from peers
         cache = sp.cache_from_map(cd[lo:hi], enc.contiguous(), gray)
-        y = sp.subm_conv_peers(ptrs, torch.bfloat16, C, w, b, cache, act="silu")
+        y = sp.subm_conv_peers(ptrs, r, torch.bfloat16, C, w, b, cache, act="silu")
         assert torch.equal(y, want[lo:hi])
     full.ctx.device_status()
 

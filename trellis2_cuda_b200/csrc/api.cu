@@ -115,17 +115,18 @@ extern "C" int t2sc_subm_conv(t2sc_ctx* ctx, t2sc_plan* plan, const void* x, con
   return row_epilogue_launch(ctx, y, rest, y, plan->n_out, Co, dtype);
 }
 
-extern "C" int t2sc_subm_conv_peers(t2sc_ctx* ctx, t2sc_plan* plan, const void* const* x_peers, int n_peers, const void* w,
-                                    const t2sc_epilogue* ep, void* y, int dtype, int Ci, int Co) {
+extern "C" int t2sc_subm_conv_peers(t2sc_ctx* ctx, t2sc_plan* plan, const void* const* x_peers, int n_peers, int self_rank,
+                                    const void* w, const t2sc_epilogue* ep, void* y, int dtype, int Ci, int Co) {
   T2_REQ(ctx, ctx && plan, "null context or plan");
   T2_REQ(ctx, n_peers >= 1 && n_peers <= 8 && x_peers, "n_peers=%d (1..8)", n_peers);
+  T2_REQ(ctx, self_rank >= 0 && self_rank < n_peers, "self_rank=%d of %d", self_rank, n_peers);
   if (plan->n_out == 0) return T2SC_OK;
   T2_REQ(ctx, w && y, "null tensor");
   for (int r = 0; r < n_peers; r++) T2_REQ(ctx, x_peers[r] && (uintptr_t)x_peers[r] % 16 == 0, "peer array %d is null or not 16-byte aligned", r);
   EpiDev e = epi_dev(ep);
   if (!conv_umma_supported(dtype, Ci, Co, e) || (e.ln && Co > 256) || plan->src)
     return t2sc_fail(ctx, T2SC_ERR_UNSUPPORTED, "peer conv needs a submanifold plan, fp16/bf16, Ci %% 64 == 0, Co %% 32 == 0, LayerNorm only for Co <= 256 (Ci=%d Co=%d dtype=%d)", Ci, Co, dtype);
-  return conv_umma_launch(ctx, plan, x_peers[0], w, Co, e, y, dtype, 0, Ci, Co, x_peers, n_peers);
+  return conv_umma_launch(ctx, plan, x_peers[self_rank], w, Co, e, y, dtype, 0, Ci, Co, x_peers, n_peers, self_rank);
 }
 
 extern "C" int t2sc_row_epilogue(t2sc_ctx* ctx, const void* x, const t2sc_epilogue* ep, void* y, int64_t n, int C, int dtype) {

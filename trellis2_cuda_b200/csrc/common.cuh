@@ -106,7 +106,7 @@ int conv_simt_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const 
                      int dtype, int Ci, int Co);
 bool conv_umma_supported(int dtype, int Ci, int Co, const EpiDev& ep);
 int conv_umma_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const void* w, i64 w_rows, const EpiDev& ep, void* y,
-                     int dtype, i64 n_in, int Ci, int Co, const void* const* x_peers = nullptr, int n_peers = 0);
+                     int dtype, i64 n_in, int Ci, int Co, const void* const* x_peers = nullptr, int n_peers = 0, int self_rank = 0);
 bool conv_umma2_supported(const t2sc_plan* plan, int dtype, int Ci, int Co, const EpiDev& ep);
 int conv_umma2_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const void* w, i64 w_rows, const EpiDev& ep, void* y,
                       int dtype, int Ci, int Co);

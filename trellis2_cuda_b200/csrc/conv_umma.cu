@@ -50,6 +50,7 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
   uint32_t* tmem_slot = (uint32_t*)(bars + 2 * S + 4 + 2 * IDX_SLOTS);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   const void** peer_base = (const void**)(tmem_slot + 2);      // the peers' array addresses (PEERS only)
+  uint32_t* slot_remote = (uint32_t*)(peer_base + 8);          // PEERS: does the tap in this index slot read any row of a peer?
 
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * S, bar_accf = bar_empty + 8 * S, bar_acce = bar_accf + 16,
@@ -60,7 +61,8 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
     const int ngw = (a.dbg_skip & 2048) ? 1 : NUM_PROD_THREADS / 32;       // measurement aid: one gather warp only
     for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, ngw * 32 + ((a.dbg_skip & 512) ? 0 : 1)); mbar_init(bar_empty + 8 * s, 1); }
     for (int b = 0; b < 2; b++) { mbar_init(bar_accf + 8 * b, 1); mbar_init(bar_acce + 8 * b, 128 * MH); }
-    for (int r = 0; r < IDX_SLOTS; r++) { mbar_init(bar_iready + 8 * r, 1); mbar_init(bar_ifree + 8 * r, ngw); }
+    for (int r = 0; r < IDX_SLOTS; r++) { mbar_init(bar_iready + 8 * r, 2); mbar_init(bar_ifree + 8 * r, ngw); }      // two index warps
+    for (int r = 0; r < 2 * IDX_SLOTS; r++) slot_remote[r] = 0;
     *abort_flag = 0;
     if (PEERS) for (int r = 0; r < 8; r++) peer_base[r] = a.xp[r];
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -82,7 +84,7 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
   if (warp < 4) {
     if ((a.dbg_skip & 2048) && warp > 0) goto role_done;
     // ===================================================================== A producer: gather rows into the swizzled tile
-    const T* x = (const T*)a.x;
+    const T* x = (const T*)a.x;          // PEERS: the local array, xp[self_rank]
     const int t = threadIdx.x, jbase = t >> 3, c16 = t & 7;
     const uint32_t dst_thread = (uint32_t)(jbase * 128 + ((c16 ^ (jbase & 7)) << 4));   // (jbase + 16 i) & 7 == jbase & 7
     uint32_t it = 0, iit = 0;
@@ -96,16 +98,29 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
         const uint32_t slot = iit % IDX_SLOTS, iph = (iit / IDX_SLOTS) & 1;
         const bool noring = a.dbg_skip & 128;
         if (!noring) mbar_wait_t(bar_iready + 8 * slot, iph, abort_flag, a.status, 32, prof, w_idx);
-        uint32_t idx[8 * MH];       // rows jbase + 16 i; rows 128.. are the second half, stored right behind the first
+        // Ring entries: row number (PEERS: (owner << 29) | row), or RING_ABSENT.  Everything that does not depend on the
+        // channel chunk is done here, once per tap, so that a copy costs two instructions (address, cp.async): the gather
+        // warps run these in order and their instruction count per unit is what bounds narrow layers.
+        uint32_t idx[8 * MH], sz[8 * MH];       // rows jbase + 16 i; rows 128.. are the second half, stored right behind the first
 #pragma unroll
         for (int i = 0; i < 8 * MH; i++) idx[i] = ring[slot * ROWS + jbase + 16 * i];
-        // PEERS: entry = (owner << 29) | row.  The row addresses are formed here, once per tap: a table load between the
+        // PEERS: almost every tap reads local rows only (the index warp says so per slot) and takes the plain path with the
+        // owner bits masked off.  For a tap with rows of a peer the addresses are formed here: a table load between the
         // copies below would be ordered after each of them and serialise the loop.
         const T* rp[PEERS ? 8 * MH : 1];
+        bool remote = false;
         if constexpr (PEERS) {
+          remote = (slot_remote[2 * slot] | slot_remote[2 * slot + 1]) != 0;
+          if (__builtin_expect(remote, 0)) {
 #pragma unroll
-          for (int i = 0; i < 8 * MH; i++)
-            rp[i] = idx[i] != NBR_EMPTY ? (const T*)peer_base[idx[i] >> 29] + (i64)(idx[i] & 0x1FFFFFFFu) * a.Ci + c16 * 8 : nullptr;
+            for (int i = 0; i < 8 * MH; i++)
+              rp[i] = idx[i] != RING_ABSENT ? (const T*)peer_base[idx[i] >> 29] + (i64)(idx[i] & 0x1FFFFFFFu) * a.Ci + c16 * 8 : x;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8 * MH; i++) {
+          sz[i] = (~idx[i] >> 27) & 16u;                                 // 16 bytes, or 0 = zero-fill for an absent neighbour
+          idx[i] &= PEERS ? 0x1FFFFFFFu : 0x7FFFFFFFu;                   // absent -> row 0, a valid address that is not read
         }
         __syncwarp();
         if (lane == 0 && !noring) mbar_arrive(bar_ifree + 8 * slot);       // one arrival per gather warp: arrivals on one barrier serialise
@@ -117,14 +132,12 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
           const uint32_t dst = smem_base + st * STAGE + q * UNIT + dst_thread;
           const T* xs = x + c * KCH + c16 * 8;
           if (!(a.dbg_skip & 1)) {
+            if (PEERS && __builtin_expect(remote, 0)) {          // one branch per unit, not per copy: a P2P load when the owner is a peer
 #pragma unroll
-            for (int i = 0; i < 8 * MH; i++) {
-              if constexpr (PEERS) {      // a P2P load when the owner is a peer
-                cp_async16(dst + i * (16 * 128), rp[i] ? (const void*)(rp[i] + c * KCH) : (const void*)x, rp[i] ? 16u : 0u);
-              } else {
-                const bool present = idx[i] != NBR_EMPTY;
-                cp_async16(dst + i * (16 * 128), present ? (const void*)(xs + (i64)idx[i] * a.Ci) : (const void*)x, present ? 16u : 0u);
-              }
+              for (int i = 0; i < 8 * MH; i++) cp_async16(dst + i * (16 * 128), rp[i] + c * KCH, sz[i]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8 * MH; i++) cp_async16(dst + i * (16 * 128), xs + (i64)idx[i] * a.Ci, sz[i]);
             }
           }
           if (++q == U) { cp_async_arrive_noinc(bar_full + 8 * st); q = 0; it++; }   // this thread's arrival, delivered when its copies have landed
@@ -166,18 +179,20 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
       }
     }
     __syncwarp();
-  } else if (warp == WARP_IDX) {
+  } else if (warp == WARP_IDX || warp == warp_idx2(MH)) {
     // ===================================================================== neighbour indices, one ring slot per (tile, tap)
+    // Two index warps, each serving half of the tile's rows (their per-tap instruction path is as critical as the gather warps').
+    const int ih = warp == WARP_IDX ? 0 : 1;
     // Runs ahead of the gather warps across tile boundaries, so a new tile starts without a dependent-load bubble.
     // The loads of one round of IDX_ROUND taps are all in flight before the previous round is handed over, and the
     // next tile's row numbers are fetched while this tile's taps are served: the warp is never one load latency per tap.
-    constexpr int NR = 4 * MH;
+    constexpr int NR = ROWS / 64, HROWS = ROWS / 2;
     uint32_t iit = 0;
     const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_free = 0, w_load = 0, t_role = clock64();
     auto rows_of = [&](const PlanTile& tl, int* nr) {
 #pragma unroll
       for (int i = 0; i < NR; i++) {
-        const int j = lane + 32 * i;
+        const int j = ih * HROWS + lane + 32 * i;
         nr[i] = -1;
         if (j < tl.rows) { const int r = a.order[tl.start + j]; nr[i] = a.src ? (a.src[r] >> 3) : r; }
       }
@@ -200,7 +215,14 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
         mbar_wait_t(bar_ifree + 8 * slot, iph ^ 1, abort_flag, a.status, 64, prof, w_free);
         if (prof) { long long t0 = clock64(); volatile uint32_t sink = val[q][0]; (void)sink; w_load += clock64() - t0; }
 #pragma unroll
-        for (int i = 0; i < NR; i++) ring[slot * ROWS + lane + 32 * i] = val[q][i];
+        for (int i = 0; i < NR; i++) ring[slot * ROWS + ih * HROWS + lane + 32 * i] = val[q][i] == NBR_EMPTY ? RING_ABSENT : val[q][i];
+        if constexpr (PEERS) {
+          bool rem = false;
+#pragma unroll
+          for (int i = 0; i < NR; i++) rem |= val[q][i] != NBR_EMPTY && (int)(val[q][i] >> 29) != a.self_rank;
+          rem = __any_sync(0xffffffffu, rem);
+          if (lane == 0) slot_remote[2 * slot + ih] = rem;
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_iready + 8 * slot);
         iit++;
@@ -229,7 +251,7 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
       for (int i = 0; i < NR; i++) nr[i] = nr_next[i];
       tile_n0 = tile_n1; tile_n1 = tile_n2;
     }
-    if (prof && blockIdx.x == 0 && lane == 0)
+    if (prof && blockIdx.x == 0 && lane == 0 && ih == 0)
       printf("[t2sc prof] index warp: total %lld clk, wait slot free %lld, wait own loads %lld, slots %u\n", clock64() - t_role, w_free, w_load, iit);
   } else if (warp == WARP_MMA) {
     // ===================================================================== MMA issuer: one lane waits, issues and commits
@@ -380,7 +402,7 @@ bool conv_umma_supported(int dtype, int Ci, int Co, const EpiDev& ep) {
 }
 
 int conv_umma_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const void* w, i64 w_rows, const EpiDev& ep, void* y,
-                     int dtype, i64 n_in, int Ci, int Co, const void* const* x_peers, int n_peers) {
+                     int dtype, i64 n_in, int Ci, int Co, const void* const* x_peers, int n_peers, int self_rank) {
   T2_CUDA(ctx, cudaSetDevice(ctx->device));
   const int BN = pick_bn(Co);
   T2_REQ(ctx, BN > 0, "Co=%d", Co);
@@ -401,7 +423,7 @@ int conv_umma_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const 
   (void)n_in;
   static const int dbg_skip = [] { const char* e = getenv("T2SC_DEBUG_SKIP"); return e ? atoi(e) : 0; }();
   args.dbg_skip = dbg_skip | ((dbg_skip & (128 | 512 | 1024 | 2048)) ? (1 | 2 | 4 | 32 | 64) : 0);   // handshake experiments never touch data
-  args.npeers = n_peers;
+  args.npeers = n_peers; args.self_rank = self_rank;
   for (int r = 0; r < 8; r++) args.xp[r] = r < n_peers ? x_peers[r] : nullptr;
   args.x = x; args.y = y; args.nbr = plan->nbr; args.order = plan->order; args.src = plan->src;
   args.tiles = plan->tiles; args.ntiles = plan->ntiles; args.status = ctx->status;

@@ -17,6 +17,7 @@ constexpr bool kProfileWaits = true;     // diagnostic build (python -m trellis2
 constexpr bool kProfileWaits = false;
 #endif
 constexpr int IDX_SLOTS = 8;
+constexpr uint32_t RING_ABSENT = 0x80000000u;      // index-ring entry of an absent neighbour (row numbers are below 2^30)
 #ifndef T2SC_IDX_ROUND
 #define T2SC_IDX_ROUND 1      // measured: 1 is as fast as 2 or 4 with 128-row tiles and faster with 256-row tiles
 #endif
@@ -24,7 +25,9 @@ constexpr int IDX_ROUND = T2SC_IDX_ROUND;          // taps whose index loads are
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // ~2 s at boost clock
 constexpr int SMEM_BUDGET = 227 * 1024;
 
-__host__ __device__ constexpr int num_threads(int MH) { return (7 + 4 * MH) * 32; }
+// warps: 4 gather, weights, indices, MMA, 4 per 128-row half for the epilogue, and a second index warp (each serves half the rows)
+__host__ __device__ constexpr int num_threads(int MH) { return (8 + 4 * MH) * 32; }
+__host__ __device__ constexpr int warp_idx2(int MH) { return 7 + 4 * MH; }
 __host__ __device__ constexpr int stage_bytes(int BN, int MH) { return MH * A_BYTES + BN * 128; }
 __host__ __device__ constexpr int aux_bytes(int MH) { return IDX_SLOTS * MH * TILE_M * 4 + 512; }
 __host__ __device__ constexpr int num_stages(int BN, int MH, int U = 1) {
@@ -40,7 +43,7 @@ struct ConvArgs {
   const void* x; void* y; const uint32_t* nbr; const int* order; const int* src;
   const PlanTile* tiles; const int* ntiles; int* status;
   int Ci, Co, n_cot, is_bf16;
-  int npeers;               // > 0: map entries are (owner << 29) | row and rows are read from xp[owner]
+  int npeers, self_rank;    // npeers > 0: map entries are (owner << 29) | row and rows are read from xp[owner]; xp[self_rank] is local
   const void* xp[8];
   int dbg_skip;      // measurement aid (T2SC_DEBUG_SKIP): 1 = no A gather, 2 = no B load, 4 = no MMA (results are then invalid), 8 = CTA 0 prints where each role waited
   EpiDev ep;

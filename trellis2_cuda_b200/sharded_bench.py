@@ -84,7 +84,7 @@ def run(args, rank, world, local_rank, METRIC, peaks, ClockSampler, visible_gpu_
             if timers:
                 timers[1][l].record()
             if p2p:
-                sp.subm_conv_peers(ptrs[a.data_ptr()], td, C, ws[l], None, cache, out=b[:plan.n_own])
+                sp.subm_conv_peers(ptrs[a.data_ptr()], rank, td, C, ws[l], None, cache, out=b[:plan.n_own])
             else:
                 sp.subm_conv_local(a, ws[l], None, cache, out=b[:plan.n_own])
             a, b = b, a

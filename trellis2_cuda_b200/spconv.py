@@ -200,17 +200,17 @@ def subm_conv_local(x: torch.Tensor, w: torch.Tensor, b, c: SpConvCache, **kw) -
                  kw.get("variant", "auto"), kw.get("out"))
 
 
-def subm_conv_peers(x_ptrs, x_dtype, Ci: int, w: torch.Tensor, b, c: SpConvCache, *, ln=None, act=None, residual=None, out=None):
+def subm_conv_peers(x_ptrs, rank: int, x_dtype, Ci: int, w: torch.Tensor, b, c: SpConvCache, *, ln=None, act=None, residual=None, out=None):
     """subm_conv for one rank of a Morton-range partition whose neighbour map holds (owner << 29) | row entries:
     the rows are gathered straight from the peers' feature arrays (`x_ptrs[r]` = device address of rank r's array
-    mapped into this process), so no halo is packed or exchanged.  Returns [c.N, Co]."""
+    mapped into this process, `x_ptrs[rank]` the local one), so no halo is packed or exchanged.  Returns [c.N, Co]."""
     _chk(w, "w", x_dtype, 3)
     Co = w.shape[0]
     plan = c.plan_for(Co)
     y = out if out is not None else torch.empty((plan.n_out, Co), dtype=x_dtype, device=w.device)
     e, keep = _epilogue(Co, x_dtype, b, ln, act, residual, None)
     arr = (ctypes.c_void_p * len(x_ptrs))(*[int(p) for p in x_ptrs])
-    c.ctx.check(c.ctx.lib.t2sc_subm_conv_peers(c.ctx.h, plan.h, arr, len(x_ptrs), _ptr(w), ctypes.byref(e), _ptr(y), _DT[x_dtype], Ci, Co))
+    c.ctx.check(c.ctx.lib.t2sc_subm_conv_peers(c.ctx.h, plan.h, arr, len(x_ptrs), int(rank), _ptr(w), ctypes.byref(e), _ptr(y), _DT[x_dtype], Ci, Co))
     return y
 
 
