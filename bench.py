@@ -291,7 +291,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg5"])
     ap.add_argument("--layers", type=int, default=4)
-    ap.add_argument("--halo", default="p2p", choices=["p2p", "nccl"], help="cfg5: halo rows by peer-memory loads inside the conv, or by NCCL all-to-all")
+    ap.add_argument("--halo", default="nccl", choices=["p2p", "nccl"], help="cfg5: halo rows by peer-memory loads inside the conv, or by NCCL all-to-all")
     ap.add_argument("--profile", action="store_true", help="timed steps only (no end-to-end leg, no CPU baseline): for runs under ncu")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
