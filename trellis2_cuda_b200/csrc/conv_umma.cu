@@ -9,17 +9,23 @@
 //     same weight slab, which halves the L2 -> SM weight traffic of the 128-row schedule;
 //   * warps 0-3 gather the A operand: one 16-byte cp.async per (row, 8 channels), zero-filled for absent
 //     neighbours, written straight into the 128-byte-swizzled K-major layout tcgen05 reads.  (TMA
-//     tile::gather4 was measured for this job and moves 128-byte rows three times slower.)
-//   * warp 5 feeds them neighbour indices through a small ring, one slot per (tile, tap), running ahead
-//     across tile boundaries so that a new tile starts without a chain of dependent loads;
-//   * warp 4 streams the B operand (the tap's [BN x 64] weight slab) with a 3-D TMA tile load from the
-//     weights in their checkpoint layout [Co,27,Ci] - no re-layout, no cluster multicast;
-//   * warp 6 issues tcgen05.mma (M=128, N=BN, K=16) per half into TMEM and releases smem stages /
+//     tile::gather4 was measured for this job and moves 128-byte rows three times slower.)  Everything that
+//     does not depend on the channel chunk is done once per tap, so a copy is two instructions;
+//   * warp 5 and the last warp feed them neighbour indices through a small ring, one slot per (tile, tap),
+//     each serving half of the tile's rows and running ahead across tile boundaries so that a new tile
+//     starts without a chain of dependent loads;
+//   * one lane of warp 4 streams the B operand (the tap's [BN x 64] weight slab) with a 3-D TMA tile load
+//     from the weights in their checkpoint layout [Co,27,Ci] - no re-layout, no cluster multicast;
+//   * one lane of warp 6 issues tcgen05.mma (M=128, N=BN, K=16) per half into TMEM and releases smem stages /
 //     publishes accumulators with tcgen05.commit; when 2*MH*BN <= 512 columns the accumulators are double
 //     buffered so the epilogue of one tile overlaps the main loop of the next;
 //   * 4*MH epilogue warps drain the accumulators with tcgen05.ld and apply the fused epilogue (bias,
 //     LayerNorm, activation, residual, skip) with the reference's rounding points, one thread per output
 //     row, and scatter rows back to the caller's order.
+//
+// The roles run their instructions in order, and their per-unit instruction paths (not the pipeline depth) bound
+// the narrow layers: every role keeps its loop short, fetches the next tile's descriptor early and branches once
+// per unit at most.
 //
 // Every mbarrier wait is bounded: a wait that runs out sets the context's status word, the CTA stops
 // blocking, drains and frees its TMEM; the host reports T2SC_ERR_DEVICE.
@@ -29,8 +35,8 @@ namespace {
 using namespace umma;
 
 // ------------------------------------------------------------------------------------------ kernel
-// Warp roles: 0-3 gather A (cp.async), 4 weights (TMA), 5 neighbour-index ring, 6 MMA issue + TMEM owner,
-// 7.. epilogue (4 warps per 128-row half).
+// Warp roles: 0-3 gather A (cp.async), 4 weights (TMA), 5 and the last warp neighbour-index ring, 6 MMA issue + TMEM
+// owner, 7.. epilogue (4 warps per 128-row half).
 // U = (tap, 64-channel chunk) units per pipeline stage: 1, or 2 for narrow layers, where one unit is too little work
 // for the cost of a barrier round trip.
 template <int BN, int MH, int U, bool PEERS, class T>
