@@ -187,7 +187,7 @@ def run_ours(args, rank, world, local_rank):
 
     def step(record=None):
         cache = sp.build_neighbors(coords, want_sorted=False)
-        _ = cache.plan_for(Co)                          # the schedule this conv will use (tile height depends on Co and N)
+        _ = cache.plan_for(Co, Ci)                        # the schedule this conv will use (tile height depends on Co and N)
         if record:
             record[0].record()
         y = sp.subm_conv(x, w, None, cache)
@@ -196,7 +196,7 @@ def run_ours(args, rank, world, local_rank):
         return cache, y
 
     cache, y = step()
-    st = cache.plan_for(Co).stats()
+    st = cache.plan_for(Co, Ci).stats()
     T = st["active_taps"]
     flops = 2.0 * T * Ci * Co
     ev = lambda: torch.cuda.Event(enable_timing=True)

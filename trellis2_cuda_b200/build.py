@@ -33,7 +33,7 @@ def build_library(force: bool = False, verbose: bool = False, profile_waits: boo
         return LIB
     os.makedirs(OBJ, exist_ok=True)
     extra = (["-Xptxas", "-v"] if verbose else []) + (["-DT2SC_PROFILE_WAITS"] if profile_waits else [])
-    extra += os.environ.get("T2SC_NVCC_FLAGS", "").split()          # experiments, e.g. -DT2SC_IDX_ROUND=2
+    extra += os.environ.get("T2SC_NVCC_FLAGS", "").split()          # experiments, e.g. -DT2SC_IDX_BATCH=2
 
     def cc(src):
         obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")

@@ -37,13 +37,15 @@ using namespace umma;
 // ------------------------------------------------------------------------------------------ kernel
 // Warp roles: 0-3 gather A (cp.async), 4 weights (TMA), 5 and the last warp neighbour-index ring, 6 MMA issue + TMEM
 // owner, 7.. epilogue (4 warps per 128-row half).
-// U = (tap, 64-channel chunk) units per pipeline stage: 1, or 2 for narrow layers, where one unit is too little work
-// for the cost of a barrier round trip.
-template <int BN, int MH, int U, bool PEERS, class T>
-__global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_constant__ CUtensorMap tmw, const ConvArgs a) {
-  constexpr int UNIT = stage_bytes(BN, MH);          // one unit: MH gathered A halves + one weight slab
-  constexpr int STAGE = U * UNIT;
-  constexpr int S = num_stages(BN, MH, U);
+// One pipeline stage holds one unit = one (tap, 64-channel chunk).
+// G = gather groups of four warps.  G = 1: the four gather warps fill every unit together.  G = 2 (128-row tiles):
+// a second group of four warps sits behind the epilogue warps and the groups fill alternate units, so one group's
+// barrier round trips and index reads overlap the other group's copies.
+template <int BN, int MH, int G, bool PEERS, class T>
+__global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __grid_constant__ CUtensorMap tmw, const ConvArgs a) {
+  static_assert(G == 1 || (G == 2 && MH == 1), "a second gather group only fits beside 128-row tiles");
+  constexpr int STAGE = stage_bytes(BN, MH);         // MH gathered A halves + one weight slab
+  constexpr int S = num_stages(BN, MH);
   constexpr int B_BYTES = BN * 128;
   constexpr int NB = num_acc_bufs(BN, MH);            // accumulator buffers, each MH halves of BN columns
   constexpr int TMEM_COLS = NB * MH * BN < 32 ? 32 : NB * MH * BN;
@@ -62,12 +64,14 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
   const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * S, bar_accf = bar_empty + 8 * S, bar_acce = bar_accf + 16,
                  bar_iready = bar_acce + 16, bar_ifree = bar_iready + 8 * IDX_SLOTS;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nchunk = a.Ci / KCH;
 
   if (threadIdx.x == 0) {
     const int ngw = (a.dbg_skip & 2048) ? 1 : NUM_PROD_THREADS / 32;       // measurement aid: one gather warp only
     for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, ngw * 32 + ((a.dbg_skip & 512) ? 0 : 1)); mbar_init(bar_empty + 8 * s, 1); }
     for (int b = 0; b < 2; b++) { mbar_init(bar_accf + 8 * b, 1); mbar_init(bar_acce + 8 * b, 128 * MH); }
-    for (int r = 0; r < IDX_SLOTS; r++) { mbar_init(bar_iready + 8 * r, 2); mbar_init(bar_ifree + 8 * r, ngw); }      // two index warps
+    // two index warps fill a slot; with G = 2 every unit of the tap is read by its own group: nchunk reads of 4 warps each
+    for (int r = 0; r < IDX_SLOTS; r++) { mbar_init(bar_iready + 8 * r, 2); mbar_init(bar_ifree + 8 * r, G == 2 ? 4 * nchunk : ngw); }
     for (int r = 0; r < 2 * IDX_SLOTS; r++) slot_remote[r] = 0;
     *abort_flag = 0;
     if (PEERS) for (int r = 0; r < 8; r++) peer_base[r] = a.xp[r];
@@ -85,9 +89,8 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
 
   const int ntiles = *a.ntiles;
   const int nitems = ntiles * a.n_cot;
-  const int nchunk = a.Ci / KCH;
 
-  if (warp < 4) {
+  if (warp < 4 && G == 1) {
     if ((a.dbg_skip & 2048) && warp > 0) goto role_done;
     // ===================================================================== A producer: gather rows into the swizzled tile
     const T* x = (const T*)a.x;          // PEERS: the local array, xp[self_rank]
@@ -99,7 +102,6 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
       const PlanTile tile = tile_next;
       if (item + (int)gridDim.x < nitems) tile_next = a.tiles[(item + gridDim.x) / a.n_cot];     // in flight while this tile is gathered
-      int q = 0; uint32_t st = 0;
       for (uint32_t mk = tile.mask; mk; mk &= mk - 1, iit++) {
         const uint32_t slot = iit % IDX_SLOTS, iph = (iit / IDX_SLOTS) & 1;
         const bool noring = a.dbg_skip & 128;
@@ -130,12 +132,10 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
         }
         __syncwarp();
         if (lane == 0 && !noring) mbar_arrive(bar_ifree + 8 * slot);       // one arrival per gather warp: arrivals on one barrier serialise
-        for (int c = 0; c < nchunk; c++) {
-          if (q == 0) {
-            st = it % S;
-            mbar_wait_t(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 1, prof, w_empty);
-          }
-          const uint32_t dst = smem_base + st * STAGE + q * UNIT + dst_thread;
+        for (int c = 0; c < nchunk; c++, it++) {
+          const uint32_t st = it % S;
+          mbar_wait_t(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 1, prof, w_empty);
+          const uint32_t dst = smem_base + st * STAGE + dst_thread;
           const T* xs = x + c * KCH + c16 * 8;
           if (!(a.dbg_skip & 1)) {
             if (PEERS && __builtin_expect(remote, 0)) {          // one branch per unit, not per copy: a P2P load when the owner is a peer
@@ -146,14 +146,66 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
               for (int i = 0; i < 8 * MH; i++) cp_async16(dst + i * (16 * 128), xs + (i64)idx[i] * a.Ci, sz[i]);
             }
           }
-          if (++q == U) { cp_async_arrive_noinc(bar_full + 8 * st); q = 0; it++; }   // this thread's arrival, delivered when its copies have landed
+          cp_async_arrive_noinc(bar_full + 8 * st);     // this thread's arrival, delivered when its copies have landed
         }
       }
-      if (q != 0) { cp_async_arrive_noinc(bar_full + 8 * st); it++; }                // last, partly filled stage of the item
     }
     cp_async_wait_all();
     if (prof && blockIdx.x == 0 && threadIdx.x == 0)
-      printf("[t2sc prof] gather: total %lld clk, wait index ring %lld, wait stage free %lld, stages %u\n", clock64() - t_role, w_idx, w_empty, it);
+      printf("[t2sc prof] gather: total %lld clk, wait index ring %lld, wait stage free %lld, units %u\n", clock64() - t_role, w_idx, w_empty, it);
+  } else if (G == 2 && (warp < 4 || warp >= warp_group2(MH))) {
+    // ===================================================================== A producer, two groups filling alternate units
+    const int g = warp < 4 ? 0 : 1;
+    const T* x = (const T*)a.x;
+    const int t = (threadIdx.x & 127), jbase = t >> 3, c16 = t & 7;          // both groups start at a multiple of 128 threads
+    const uint32_t dst_thread = (uint32_t)(jbase * 128 + ((c16 ^ (jbase & 7)) << 4));
+    uint32_t it = 0, iit = 0;
+    PlanTile tile_next = blockIdx.x < nitems ? a.tiles[blockIdx.x / a.n_cot] : PlanTile{};
+    for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+      const PlanTile tile = tile_next;
+      if (item + (int)gridDim.x < nitems) tile_next = a.tiles[(item + gridDim.x) / a.n_cot];
+      for (uint32_t mk = tile.mask; mk; mk &= mk - 1, iit++) {
+        for (int c = 0; c < nchunk; c++, it++) {
+          if ((int)(it & 1) != g) continue;
+          const uint32_t slot = iit % IDX_SLOTS, iph = (iit / IDX_SLOTS) & 1, st = it % S;
+          mbar_wait(bar_iready + 8 * slot, iph, abort_flag, a.status, 32);
+          uint32_t idx[8], sz[8];
+#pragma unroll
+          for (int i = 0; i < 8; i++) idx[i] = ring[slot * ROWS + jbase + 16 * i];
+          const T* rp[PEERS ? 8 : 1];
+          bool remote = false;
+          if constexpr (PEERS) {
+            remote = (slot_remote[2 * slot] | slot_remote[2 * slot + 1]) != 0;
+            if (__builtin_expect(remote, 0)) {
+#pragma unroll
+              for (int i = 0; i < 8; i++)
+                rp[i] = idx[i] != RING_ABSENT ? (const T*)peer_base[idx[i] >> 29] + (i64)(idx[i] & 0x1FFFFFFFu) * a.Ci + c16 * 8 : x;
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            sz[i] = (~idx[i] >> 27) & 16u;
+            idx[i] &= PEERS ? 0x1FFFFFFFu : 0x7FFFFFFFu;
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_ifree + 8 * slot);
+          mbar_wait(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 1);
+          const uint32_t dst = smem_base + st * STAGE + dst_thread;
+          const T* xs = x + c * KCH + c16 * 8;
+          if (!(a.dbg_skip & 1)) {
+            if (PEERS && __builtin_expect(remote, 0)) {
+#pragma unroll
+              for (int i = 0; i < 8; i++) cp_async16(dst + i * (16 * 128), rp[i] + c * KCH, sz[i]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; i++) cp_async16(dst + i * (16 * 128), xs + (i64)idx[i] * a.Ci, sz[i]);
+            }
+          }
+          cp_async_arrive_noinc(bar_full + 8 * st);
+        }
+      }
+    }
+    cp_async_wait_all();
   } else if (warp == WARP_TMA) {
     // ===================================================================== B producer (weights by TMA): one lane does it all
     if (lane == 0 && !(a.dbg_skip & 512)) {
@@ -164,24 +216,18 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
         const PlanTile tile = tile_next;
         if (item + (int)gridDim.x < nitems) tile_next = a.tiles[(item + gridDim.x) / a.n_cot];
         const int wrow = tile.wbase * a.Co + cot * BN;
-        const int nunits = __popc(tile.mask) * nchunk;
-        int q = 0, u = 0; uint32_t st = 0;
         for (uint32_t mk = tile.mask; mk; mk &= mk - 1) {
           const int v = __ffs(mk) - 1;
-          for (int c = 0; c < nchunk; c++, u++) {
-            if (q == 0) {
-              st = it % S;
-              mbar_wait(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 2);
-              const int nq = nunits - u < U ? nunits - u : U;
-              if (a.dbg_skip & 2) mbar_arrive(bar_full + 8 * st);
-              else mbar_arrive_expect_tx(bar_full + 8 * st, nq * B_BYTES);
+          for (int c = 0; c < nchunk; c++, it++) {
+            const uint32_t st = it % S;
+            mbar_wait(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 2);
+            if (a.dbg_skip & 2) mbar_arrive(bar_full + 8 * st);
+            else {
+              mbar_arrive_expect_tx(bar_full + 8 * st, B_BYTES);
+              tma_load_3d(smem_base + st * STAGE + MH * A_BYTES, &tmw, c * KCH, v, wrow, bar_full + 8 * st);
             }
-            if (!(a.dbg_skip & 2))
-              tma_load_3d(smem_base + st * STAGE + q * UNIT + MH * A_BYTES, &tmw, c * KCH, v, wrow, bar_full + 8 * st);
-            if (++q == U) { q = 0; it++; }
           }
         }
-        if (q != 0) it++;
       }
     }
     __syncwarp();
@@ -190,7 +236,7 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
     // Two index warps, each serving half of the tile's rows (their per-tap instruction path is as critical as the gather warps').
     const int ih = warp == WARP_IDX ? 0 : 1;
     // Runs ahead of the gather warps across tile boundaries, so a new tile starts without a dependent-load bubble.
-    // The loads of one round of IDX_ROUND taps are all in flight before the previous round is handed over, and the
+    // The loads of one round of IDX_BATCH taps are all in flight before the previous round is handed over, and the
     // next tile's row numbers are fetched while this tile's taps are served: the warp is never one load latency per tap.
     constexpr int NR = ROWS / 64, HROWS = ROWS / 2;
     uint32_t iit = 0;
@@ -203,18 +249,18 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
         if (j < tl.rows) { const int r = a.order[tl.start + j]; nr[i] = a.src ? (a.src[r] >> 3) : r; }
       }
     };
-    auto load_round = [&](uint32_t (&val)[IDX_ROUND][NR], uint32_t& mk, const int* nr) {
+    auto load_round = [&](uint32_t (&val)[IDX_BATCH][NR], uint32_t& mk, const int* nr) {
 #pragma unroll
-      for (int q = 0; q < IDX_ROUND; q++) {
+      for (int q = 0; q < IDX_BATCH; q++) {
         if (!mk) break;
         const int v = __ffs(mk) - 1; mk &= mk - 1;
 #pragma unroll
         for (int i = 0; i < NR; i++) val[q][i] = (nr[i] < 0 || (a.dbg_skip & 32)) ? NBR_EMPTY : __ldg(a.nbr + (i64)nr[i] * 27 + v);
       }
     };
-    auto retire_round = [&](const uint32_t (&val)[IDX_ROUND][NR], uint32_t& mk) {
+    auto retire_round = [&](const uint32_t (&val)[IDX_BATCH][NR], uint32_t& mk) {
 #pragma unroll
-      for (int q = 0; q < IDX_ROUND; q++) {
+      for (int q = 0; q < IDX_BATCH; q++) {
         if (!mk) break;
         mk &= mk - 1;
         const uint32_t slot = iit % IDX_SLOTS, iph = (iit / IDX_SLOTS) & 1;
@@ -244,7 +290,7 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
       const PlanTile tile_n2 = desc_of(item + 2 * gridDim.x);
       rows_of(tile_n1, nr_next);                               // in flight while this tile is served
       uint32_t mk_load = tile.mask, mk_ret = tile.mask;
-      uint32_t va[IDX_ROUND][NR], vb[IDX_ROUND][NR];
+      uint32_t va[IDX_BATCH][NR], vb[IDX_BATCH][NR];
       load_round(va, mk_load, nr);
       while (mk_ret) {
         load_round(vb, mk_load, nr);
@@ -275,21 +321,20 @@ __global__ void __launch_bounds__(num_threads(MH), 1) k_conv_umma(const __grid_c
         const uint32_t d_tmem = tmem_base + buf * (MH * BN);
         const int halves = tile.rows > TILE_M ? MH : 1;
         const int nunits = __popc(tile.mask) * nchunk;
-        for (int u0 = 0; u0 < nunits; u0 += U, it++) {
+        for (int u = 0; u < nunits; u++, it++) {
           const uint32_t s = it % S, ph = (it / S) & 1;
           // No tcgen05 fence after this wait (the operands are shared-memory data published by the barrier, not tcgen05
           // results) and no proxy fence either: the copies' completion is delivered through the barrier itself
           // (cp.async.mbarrier.arrive.noinc); a fence.proxy.async here was measured at 3-12 % of the kernel time.
           mbar_wait_t(bar_full + 8 * s, ph, abort_flag, a.status, 8, prof, w_full);
           long long ti0 = prof ? clock64() : 0;
-          const int nq = nunits - u0 < U ? nunits - u0 : U;
-          for (int q = 0; q < nq && !(a.dbg_skip & 4); q++) {
-            const uint64_t bd = umma_desc(smem_base + s * STAGE + q * UNIT + MH * A_BYTES);
+          if (!(a.dbg_skip & 4)) {
+            const uint64_t bd = umma_desc(smem_base + s * STAGE + MH * A_BYTES);
             for (int h = 0; h < halves; h++) {
-              const uint64_t ad = umma_desc(smem_base + s * STAGE + q * UNIT + h * A_BYTES);
+              const uint64_t ad = umma_desc(smem_base + s * STAGE + h * A_BYTES);
 #pragma unroll
               for (int kk = 0; kk < KCH / 16; kk++)    // +32 bytes along K inside the swizzle row = +2 in the address field
-                tc_mma(d_tmem + h * BN, ad + 2 * kk, bd + 2 * kk, idesc, (u0 + q > 0 || kk > 0) ? 1u : 0u);
+                tc_mma(d_tmem + h * BN, ad + 2 * kk, bd + 2 * kk, idesc, (u > 0 || kk > 0) ? 1u : 0u);
             }
           }
           long long ti1 = prof ? clock64() : 0;
@@ -358,29 +403,30 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-template <int BN, int MH, int U, bool PEERS, class T>
+template <int BN, int MH, int G, bool PEERS, class T>
 int launch_p(t2sc_ctx* ctx, const CUtensorMap& tm, const ConvArgs& args, i64 max_items) {
-  constexpr int smem = num_stages(BN, MH, U) * U * stage_bytes(BN, MH) + aux_bytes(MH) + 1024;
-  static_assert(smem <= SMEM_BUDGET && num_stages(BN, MH, U) >= 3, "shared memory budget");
+  constexpr int smem = num_stages(BN, MH) * stage_bytes(BN, MH) + aux_bytes(MH) + 1024;
+  static_assert(smem <= SMEM_BUDGET && num_stages(BN, MH) >= 2, "shared memory budget");
   static bool attr_set[16] = {};
   if (!attr_set[ctx->device & 15]) {
-    T2_CUDA(ctx, cudaFuncSetAttribute(k_conv_umma<BN, MH, U, PEERS, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    T2_CUDA(ctx, cudaFuncSetAttribute(k_conv_umma<BN, MH, G, PEERS, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set[ctx->device & 15] = true;
   }
   int grid = (int)(max_items < ctx->num_sms ? max_items : ctx->num_sms);
-  k_conv_umma<BN, MH, U, PEERS, T><<<grid, num_threads(MH), smem, ctx->stream>>>(tm, args);
+  k_conv_umma<BN, MH, G, PEERS, T><<<grid, num_threads(MH, G), smem, ctx->stream>>>(tm, args);
   T2_LAUNCHED(ctx);
   return T2SC_OK;
 }
 
-// One (tap, chunk) unit per stage by default; T2SC_UNITS=2 selects two (measured: no gain, kept for experiments).
-// The peer-memory form exists for 128-row and 256-row tiles with one unit per stage.
+// Gather groups: two for 64 input channels on 128-row tiles (one unit per tap: measured 16-19 % faster; equal at 128
+// channels, 3 % slower at 256), else one.  T2SC_GATHER_GROUPS=1|2 overrides; the peer-memory form has one group.
 template <int BN, int MH, class T>
 int launch_bn(t2sc_ctx* ctx, const CUtensorMap& tm, const ConvArgs& args, i64 max_items) {
-  static const int force_u = [] { const char* e = getenv("T2SC_UNITS"); return e ? atoi(e) : 0; }();
+  static const int force_g = [] { const char* e = getenv("T2SC_GATHER_GROUPS"); return e ? atoi(e) : 0; }();
   if (args.npeers > 0) return launch_p<BN, MH, 1, true, T>(ctx, tm, args, max_items);
-  if constexpr (MH == 1 && BN <= 128) {
-    if (force_u == 2) return launch_p<BN, MH, 2, false, T>(ctx, tm, args, max_items);
+  if constexpr (MH == 1) {
+    const int g = force_g ? force_g : (args.Ci == KCH ? 2 : 1);
+    if (g == 2) return launch_p<BN, MH, 2, false, T>(ctx, tm, args, max_items);
   }
   return launch_p<BN, MH, 1, false, T>(ctx, tm, args, max_items);
 }

@@ -18,16 +18,18 @@ constexpr bool kProfileWaits = false;
 #endif
 constexpr int IDX_SLOTS = 8;
 constexpr uint32_t RING_ABSENT = 0x80000000u;      // index-ring entry of an absent neighbour (row numbers are below 2^30)
-#ifndef T2SC_IDX_ROUND
-#define T2SC_IDX_ROUND 1      // measured: 1 is as fast as 2 or 4 with 128-row tiles and faster with 256-row tiles
+#ifndef T2SC_IDX_BATCH
+#define T2SC_IDX_BATCH 1      // measured: 1 is as fast as 2 or 4 with 128-row tiles and faster with 256-row tiles
 #endif
-constexpr int IDX_ROUND = T2SC_IDX_ROUND;          // taps whose index loads are issued together by the index warp
+constexpr int IDX_BATCH = T2SC_IDX_BATCH;          // taps whose index loads are issued together by the index warp
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // ~2 s at boost clock
 constexpr int SMEM_BUDGET = 227 * 1024;
 
-// warps: 4 gather, weights, indices, MMA, 4 per 128-row half for the epilogue, and a second index warp (each serves half the rows)
-__host__ __device__ constexpr int num_threads(int MH) { return (8 + 4 * MH) * 32; }
+// warps: 4 gather, weights, indices, MMA, 4 per 128-row half for the epilogue, a second index warp (each serves half the
+// rows), and with two gather groups (128-row tiles) four more gather warps, which start at thread 384 = 3 x 128
+__host__ __device__ constexpr int num_threads(int MH, int G = 1) { return (8 + 4 * MH + (G == 2 ? 4 : 0)) * 32; }
 __host__ __device__ constexpr int warp_idx2(int MH) { return 7 + 4 * MH; }
+__host__ __device__ constexpr int warp_group2(int MH) { return 8 + 4 * MH; }
 __host__ __device__ constexpr int stage_bytes(int BN, int MH) { return MH * A_BYTES + BN * 128; }
 __host__ __device__ constexpr int aux_bytes(int MH) { return IDX_SLOTS * MH * TILE_M * 4 + 512; }
 __host__ __device__ constexpr int num_stages(int BN, int MH, int U = 1) {

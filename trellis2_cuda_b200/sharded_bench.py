@@ -50,7 +50,7 @@ def run(args, rank, world, local_rank, METRIC, peaks, ClockSampler, visible_gpu_
     else:
         cache = sp.cache_from_map(coords[lo:hi], plan.nbr_local.contiguous(), gray)
     del nbr_g
-    st = cache.plan_for(C).stats()
+    st = cache.plan_for(C, C).stats()
     torch.cuda.synchronize()
     setup_ms = (time.perf_counter() - t0) * 1e3
 

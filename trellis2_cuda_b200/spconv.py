@@ -149,11 +149,12 @@ class SpConvCache:
     def plan(self) -> _Plan:
         return self.plan_for(256)
 
-    def plan_for(self, Co: int) -> _Plan:
-        """The schedule used for a conv with Co output channels, unless tile_rows was forced: 128-row tiles, except
-        256-row tiles (two accumulators per weight slab) for narrow layers on maps too large for the L2
-        (measured: 8.6 M rows at C = 128 run 3 % faster with them; 218 k rows run 10 % slower)."""
-        tr = self._tile_rows or int(os.environ.get("T2SC_TILE_ROWS", "0")) or (256 if (self.N > (1 << 18) and Co < 256) else 128)
+    def plan_for(self, Co: int, Ci: int = 0) -> _Plan:
+        """The schedule used for a conv with Ci -> Co channels, unless tile_rows was forced: 128-row tiles, except 256-row
+        tiles (two accumulators per weight slab) for layers of 128 input channels on maps too large for the L2 (measured:
+        8.6 M rows at C = 128 run 3 % faster with them; 218 k rows run 10 % slower; at 64 input channels 128-row tiles
+        with two gather groups are the fastest at every size)."""
+        tr = self._tile_rows or int(os.environ.get("T2SC_TILE_ROWS", "0")) or (256 if (self.N > (1 << 18) and Co < 256 and Ci != 64) else 128)
         if self._plan is None:
             self._plan = {}
         if tr not in self._plan:
@@ -196,7 +197,7 @@ def subm_conv_local(x: torch.Tensor, w: torch.Tensor, b, c: SpConvCache, **kw) -
     """subm_conv whose input has MORE rows than the map (owned rows first, halo rows appended); output [c.N, Co]."""
     if x.shape[0] < c.N:
         raise T2scError(-1, f"spconv shapes: x has {x.shape[0]} rows, cache has {c.N}")
-    return _conv(c.ctx, c.plan_for(w.shape[0]), x, w, b, w.shape[0], kw.get("ln"), kw.get("act"), kw.get("residual"), kw.get("skip"),
+    return _conv(c.ctx, c.plan_for(w.shape[0], w.shape[2]), x, w, b, w.shape[0], kw.get("ln"), kw.get("act"), kw.get("residual"), kw.get("skip"),
                  kw.get("variant", "auto"), kw.get("out"))
 
 
@@ -206,7 +207,7 @@ def subm_conv_peers(x_ptrs, rank: int, x_dtype, Ci: int, w: torch.Tensor, b, c: 
     mapped into this process, `x_ptrs[rank]` the local one), so no halo is packed or exchanged.  Returns [c.N, Co]."""
     _chk(w, "w", x_dtype, 3)
     Co = w.shape[0]
-    plan = c.plan_for(Co)
+    plan = c.plan_for(Co, Ci)
     y = out if out is not None else torch.empty((plan.n_out, Co), dtype=x_dtype, device=w.device)
     e, keep = _epilogue(Co, x_dtype, b, ln, act, residual, None)
     arr = (ctypes.c_void_p * len(x_ptrs))(*[int(p) for p in x_ptrs])
@@ -261,7 +262,7 @@ def subm_conv(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], c: Sp
     (``add_``), ``skip=(x_parent, src, rep)`` (``k_add_skip``)."""
     if x.shape[0] != c.N:
         raise T2scError(-1, f"spconv shapes: x has {x.shape[0]} rows, cache has {c.N}")
-    return _conv(c.ctx, c.plan_for(w.shape[0]), x, w, b, w.shape[0], ln, act, residual, skip, variant, out)
+    return _conv(c.ctx, c.plan_for(w.shape[0], w.shape[2]), x, w, b, w.shape[0], ln, act, residual, skip, variant, out)
 
 
 @dataclasses.dataclass
