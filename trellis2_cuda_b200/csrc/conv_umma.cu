@@ -97,6 +97,7 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
     const int t = threadIdx.x, jbase = t >> 3, c16 = t & 7;
     const uint32_t dst_thread = (uint32_t)(jbase * 128 + ((c16 ^ (jbase & 7)) << 4));   // (jbase + 16 i) & 7 == jbase & 7
     uint32_t it = 0, iit = 0;
+    bool alive = true;
     const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_idx = 0, w_empty = 0, t_role = clock64();
     PlanTile tile_next = blockIdx.x < nitems ? a.tiles[blockIdx.x / a.n_cot] : PlanTile{};
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
@@ -105,7 +106,7 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
       for (uint32_t mk = tile.mask; mk; mk &= mk - 1, iit++) {
         const uint32_t slot = iit % IDX_SLOTS, iph = (iit / IDX_SLOTS) & 1;
         const bool noring = a.dbg_skip & 128;
-        if (!noring) mbar_wait_t(bar_iready + 8 * slot, iph, abort_flag, a.status, 32, prof, w_idx);
+        if (!noring) alive &= mbar_wait_t(bar_iready + 8 * slot, iph, abort_flag, a.status, 32, prof, w_idx);
         // Ring entries: row number (PEERS: (owner << 29) | row), or RING_ABSENT.  Everything that does not depend on the
         // channel chunk is done here, once per tap, so that a copy costs two instructions (address, cp.async): the gather
         // warps run these in order and their instruction count per unit is what bounds narrow layers.
@@ -134,10 +135,10 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
         if (lane == 0 && !noring) mbar_arrive(bar_ifree + 8 * slot);       // one arrival per gather warp: arrivals on one barrier serialise
         for (int c = 0; c < nchunk; c++, it++) {
           const uint32_t st = it % S;
-          mbar_wait_t(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 1, prof, w_empty);
+          alive &= mbar_wait_t(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 1, prof, w_empty);
           const uint32_t dst = smem_base + st * STAGE + dst_thread;
           const T* xs = x + c * KCH + c16 * 8;
-          if (!(a.dbg_skip & 1)) {
+          if (alive && !(a.dbg_skip & 1)) {      // after a wait was given up the ring may hold anything: no more loads
             if (PEERS && __builtin_expect(remote, 0)) {          // one branch per unit, not per copy: a P2P load when the owner is a peer
 #pragma unroll
               for (int i = 0; i < 8 * MH; i++) cp_async16(dst + i * (16 * 128), rp[i] + c * KCH, sz[i]);
@@ -160,15 +161,18 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
     const int t = (threadIdx.x & 127), jbase = t >> 3, c16 = t & 7;          // both groups start at a multiple of 128 threads
     const uint32_t dst_thread = (uint32_t)(jbase * 128 + ((c16 ^ (jbase & 7)) << 4));
     uint32_t it = 0, iit = 0;
+    bool alive = true;
     PlanTile tile_next = blockIdx.x < nitems ? a.tiles[blockIdx.x / a.n_cot] : PlanTile{};
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
       const PlanTile tile = tile_next;
       if (item + (int)gridDim.x < nitems) tile_next = a.tiles[(item + gridDim.x) / a.n_cot];
       for (uint32_t mk = tile.mask; mk; mk &= mk - 1, iit++) {
         for (int c = 0; c < nchunk; c++, it++) {
+          // A group waits on units two apart, never more than the stage count apart: it cannot run two phases ahead of a
+          // stage, where a parity wait would pass by mistake.  (Alternating whole taps breaks exactly that.)
           if ((int)(it & 1) != g) continue;
           const uint32_t slot = iit % IDX_SLOTS, iph = (iit / IDX_SLOTS) & 1, st = it % S;
-          mbar_wait(bar_iready + 8 * slot, iph, abort_flag, a.status, 32);
+          alive &= mbar_wait(bar_iready + 8 * slot, iph, abort_flag, a.status, 32);
           uint32_t idx[8], sz[8];
 #pragma unroll
           for (int i = 0; i < 8; i++) idx[i] = ring[slot * ROWS + jbase + 16 * i];
@@ -189,10 +193,10 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_ifree + 8 * slot);
-          mbar_wait(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 1);
+          alive &= mbar_wait(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 1);
           const uint32_t dst = smem_base + st * STAGE + dst_thread;
           const T* xs = x + c * KCH + c16 * 8;
-          if (!(a.dbg_skip & 1)) {
+          if (alive && !(a.dbg_skip & 1)) {
             if (PEERS && __builtin_expect(remote, 0)) {
 #pragma unroll
               for (int i = 0; i < 8; i++) cp_async16(dst + i * (16 * 128), rp[i] + c * KCH, sz[i]);

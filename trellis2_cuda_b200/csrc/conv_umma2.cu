@@ -109,12 +109,13 @@ __global__ void __launch_bounds__(P_THREADS, 1) k_conv_umma2(const __grid_consta
     const int t = threadIdx.x, jbase = t >> 3, c16 = t & 7;
     const uint32_t dst_thread = (uint32_t)(jbase * 128 + ((c16 ^ (jbase & 7)) << 4));
     uint32_t it = 0, iit = 0;
+    bool alive = true;        // false once a wait was given up: the index ring may then hold anything, so no more loads
     const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_empty = 0, w_idx = 0, t_role = clock64();
     for (int item = pair; item < nitems; item += npairs) {
       const PlanTile tile = a.tiles[item / a.n_cot];
       for (uint32_t mk = tile.mask; mk; mk &= mk - 1, iit++) {
         const uint32_t slot = iit % IDX_SLOTS, iph = (iit / IDX_SLOTS) & 1;
-        { long long t0 = clock64(); mbar_wait(bar_iready + 8 * slot, iph, abort_flag, a.status, 32); if (prof) w_idx += clock64() - t0; }
+        { long long t0 = clock64(); alive &= mbar_wait(bar_iready + 8 * slot, iph, abort_flag, a.status, 32); if (prof) w_idx += clock64() - t0; }
         uint32_t idx[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) idx[i] = ring[slot * TILE_M + jbase + 16 * i];
@@ -122,10 +123,10 @@ __global__ void __launch_bounds__(P_THREADS, 1) k_conv_umma2(const __grid_consta
         if (lane == 0) mbar_arrive(bar_ifree + 8 * slot);       // one arrival per gather warp: arrivals on one barrier serialise
         for (int c = 0; c < nchunk; c++, it++) {
           const uint32_t s = it % S, ph = (it / S) & 1;
-          { long long t0 = clock64(); mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, a.status, 1); if (prof) w_empty += clock64() - t0; }
+          { long long t0 = clock64(); alive &= mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, a.status, 1); if (prof) w_empty += clock64() - t0; }
           const uint32_t dst = smem_base + s * P_STAGE + dst_thread;
           const T* xs = x + c * KCH + c16 * 8;
-          if (!(a.dbg_skip & 1)) {
+          if (alive && !(a.dbg_skip & 1)) {
 #pragma unroll
             for (int i = 0; i < 8; i++) {
               const bool present = idx[i] != NBR_EMPTY;

@@ -80,19 +80,23 @@ __device__ __forceinline__ bool mbar_try_sleep(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  After any wait in the CTA has given up, all later waits return at once.
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-  if (mbar_try(bar, parity)) return;
+// Returns false when the wait was given up (now, or earlier by any thread of the CTA): what the barrier guards has then
+// NOT happened, and the caller must not touch memory whose address depends on it.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if (mbar_try(bar, parity)) return true;
   long long t0 = clock64();
   while (!mbar_try_sleep(bar, parity)) {
-    if (*abort_flag || clock64() - t0 > WAIT_LIMIT_CYCLES) { *abort_flag = 1; atomicOr(status, code); return; }
+    if (*abort_flag || clock64() - t0 > WAIT_LIMIT_CYCLES) { *abort_flag = 1; atomicOr(status, code); return false; }
   }
+  return true;
 }
 // measurement aid (T2SC_DEBUG_SKIP bit 3): waits that also add their duration to a per-role counter
-__device__ __forceinline__ void mbar_wait_t(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code, bool prof, long long& acc) {
-  if (!prof) { mbar_wait(bar, parity, abort_flag, status, code); return; }
+__device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code, bool prof, long long& acc) {
+  if (!prof) return mbar_wait(bar, parity, abort_flag, status, code);
   long long t0 = clock64();
-  mbar_wait(bar, parity, abort_flag, status, code);
+  const bool ok = mbar_wait(bar, parity, abort_flag, status, code);
   acc += clock64() - t0;
+  return ok;
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
