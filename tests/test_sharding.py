@@ -84,3 +84,22 @@ def test_single_rank_plan_is_identity():
     nbr[nbr == oracle.EMPTY] = -1
     plan = sharding.build_halo_plan(torch.from_numpy(nbr).to(torch.int32), 0, 1, [0, 500])
     assert plan.n_halo == 0 and np.array_equal(plan.nbr_local.numpy(), nbr)
+
+
+def test_peer_map_names_owner_and_row():
+    """The map of the peer-memory conv: (owner << 29) | row inside the owner's range, absent stays all ones."""
+    c = scenes.config1_sphere()[:3000]
+    nbr = oracle.build_neighbors(c, want_sorted=False)[0].astype(np.int64)
+    nbr[nbr == oracle.EMPTY] = -1
+    starts = sharding.partition(len(c), 3)
+    for r in range(3):
+        lo, hi = starts[r], starts[r + 1]
+        enc = sharding.peer_map(torch.from_numpy(nbr[lo:hi]).to(torch.int32), starts).numpy()
+        u = enc.astype(np.int64) & 0xFFFFFFFF
+        present = nbr[lo:hi] >= 0
+        assert (u[~present] == 0xFFFFFFFF).all()
+        owner, row = u[present] >> sharding.PEER_SHIFT, u[present] & ((1 << sharding.PEER_SHIFT) - 1)
+        assert owner.max() < 3 and (np.asarray(starts)[owner] + row == nbr[lo:hi][present]).all()
+        assert (owner != r).any() and (owner == r).sum() > 0.9 * owner.size        # a real but small halo
+    with pytest.raises(ValueError):
+        sharding.peer_map(torch.zeros((1, 27), dtype=torch.int32), list(range(10)))       # more than 8 ranks
