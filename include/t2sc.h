@@ -44,7 +44,9 @@ int t2sc_ctx_destroy(t2sc_ctx* ctx);
 int t2sc_ctx_sync(t2sc_ctx* ctx);                      /* replaces dsync(), src/core.cu:29 */
 const char* t2sc_last_error(const t2sc_ctx* ctx);      /* ctx may be NULL: error of the last failed create */
 int64_t t2sc_launch_count(const t2sc_ctx* ctx);        /* kernels of this library launched so far */
-int t2sc_device_status(t2sc_ctx* ctx, int* status_host); /* syncs; non-zero = a bounded device-side wait gave up */
+/* syncs; *status_host non-zero (and T2SC_ERR_DEVICE returned) = a bounded device-side wait gave up (bits 0-9 except 8)
+ * or a neighbour-map entry pointed outside its feature array (bit 8); the word is cleared by the call */
+int t2sc_device_status(t2sc_ctx* ctx, int* status_host);
 
 /* ---- neighbour maps.  Replaces build_neighbors (src/spconv.cu:38-54; kernels :14-36).
  * Writes nbr [n,27], gray [n] and, when `sorted` is not NULL, the reference's row order: the stable
@@ -109,6 +111,21 @@ int t2sc_add_skip(t2sc_ctx* ctx, void* h, const void* x, const int32_t* src, int
 int t2sc_plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_t* gray, int64_t n_rows,
                      const int32_t* src, int64_t m, int64_t block_rows, int tile_rows, t2sc_plan** out);
 int t2sc_plan_destroy(t2sc_ctx* ctx, t2sc_plan* plan);
+/* Declares that the entries of the plan's neighbour map index a feature array of n_in >= n_rows rows (one rank of a
+ * partitioned scene: owned rows first, the halo rows of its peers appended).  Without it n_in == n_rows, which is what
+ * the reference requires of subm_conv (REQ N == c.N, src/spconv.cu:162). */
+int t2sc_plan_set_input_rows(t2sc_ctx* ctx, t2sc_plan* plan, int64_t n_in);
+/* Plan for one rank of a partitioned scene (no counterpart in the reference, which is single-GPU).  nbr is the rank's
+ * LOCAL map over its n_rows owned rows: entries below n_own are owned rows, entries from n_own up are halo rows of its
+ * peers appended behind them.  Rows none of whose taps reads a halo row form the interior part of the plan, the others
+ * the boundary part; the boundary tiles come last.  The interior part can run (T2SC_PART_INTERIOR) while the halo rows are
+ * still on their way, the boundary part (T2SC_PART_BOUNDARY) once they have landed.  Together the two parts write every
+ * output row exactly once, with the bits t2sc_subm_conv gives on an unsplit plan. */
+int t2sc_plan_create_split(t2sc_ctx* ctx, const uint32_t* nbr, const int32_t* gray, int64_t n_rows, int64_t n_own,
+                           int64_t block_rows, int tile_rows, t2sc_plan** out);
+enum { T2SC_PART_ALL = 0, T2SC_PART_INTERIOR = 1, T2SC_PART_BOUNDARY = 2 };
+/* tiles of the two parts (syncs); a plan not made by t2sc_plan_create_split is all interior */
+int t2sc_plan_parts(t2sc_ctx* ctx, t2sc_plan* plan, int64_t* interior_tiles, int64_t* boundary_tiles);
 /* tiles, sum over tiles of rows*popcount(tile mask), sum over rows of popcount(row mask) (syncs) */
 int t2sc_plan_stats(t2sc_ctx* ctx, t2sc_plan* plan, int64_t* tiles, int64_t* computed_taps, int64_t* active_taps);
 /* internal row order of the plan, int32 [m] (for inspection and tests) */
@@ -134,19 +151,46 @@ typedef struct {
 /* Replaces subm_conv (src/spconv.cu:160-175; kernel :91-150) and, with a subdivision plan, the
  * conv1 -> k_gather_rows pair of SDecoder::up (src/sdec.cu:76-80) computing kept children only.
  * x [n_in,Ci], w [w_rows,27,Ci] (w_rows = Co, or 8*Co for a subdivision plan), y [n_out,Co] in the
- * caller's row order; Ci % 32 == 0 as in the reference.  ep may be NULL. */
+ * caller's row order; Ci % 32 == 0 as in the reference.  n_in must equal the rows the plan was made for (the
+ * reference's REQ N == c.N, src/spconv.cu:162; see t2sc_plan_set_input_rows).  A map entry that points at or past
+ * row n_in is read as an absent neighbour and reported by t2sc_device_status (T2SC_ERR_DEVICE).  ep may be NULL. */
 int t2sc_subm_conv(t2sc_ctx* ctx, t2sc_plan* plan, const void* x, const void* w, const t2sc_epilogue* ep,
                    void* y, int dtype, int64_t n_in, int Ci, int Co, int variant);
+
+/* t2sc_subm_conv over one part of a plan (T2SC_PART_*): the rows of the other part are left untouched in y. */
+int t2sc_subm_conv_part(t2sc_ctx* ctx, t2sc_plan* plan, const void* x, const void* w, const t2sc_epilogue* ep,
+                        void* y, int dtype, int64_t n_in, int Ci, int Co, int variant, int part);
 
 /* The same operator for one rank of a Morton-range partition, reading its inputs straight from its peers' memory: the
  * gather of the conv kernel itself is the halo exchange (no pack kernel, no collective in the data path).  x_peers[r]
  * is rank r's feature array [rows_r, Ci], mapped into this process (CUDA IPC / symmetric memory; x_peers[self_rank] is
- * the local array: taps whose rows are all local, nearly all of them, take the ordinary gather path); every present entry of the plan's neighbour map is (owner rank << 29) | (row within the owner's
- * array), 0xffffffff = absent.  At most 8 peers, fewer than 2^29 rows per rank.  The caller orders the ranks: a layer
- * may start only when every peer has finished writing the array it reads.  Only the tcgen05 path (fp16 / bf16,
- * Ci % 64 == 0, Co % 32 == 0).  The reference is single-GPU and has no counterpart. */
-int t2sc_subm_conv_peers(t2sc_ctx* ctx, t2sc_plan* plan, const void* const* x_peers, int n_peers, int self_rank,
-                         const void* w, const t2sc_epilogue* ep, void* y, int dtype, int Ci, int Co);
+ * the local array: taps whose rows are all local, nearly all of them, take the ordinary gather path); rows_peers[r] is
+ * the number of rows of that array.  Every present entry of the plan's neighbour map is
+ * (owner rank << T2SC_PEER_SHIFT) | (row within the owner's array), 0xffffffff = absent; an entry naming an owner
+ * >= n_peers or a row >= rows_peers[owner] is read as absent and reported by t2sc_device_status.  At most 8 peers, at
+ * most 2^28 rows per rank.  The caller orders the ranks: a layer may start only when every peer has finished writing
+ * the array it reads.  Only the tcgen05 path (fp16 / bf16, Ci % 64 == 0, Co % 32 == 0).  The reference is single-GPU
+ * and has no counterpart. */
+#define T2SC_PEER_SHIFT 28
+int t2sc_subm_conv_peers(t2sc_ctx* ctx, t2sc_plan* plan, const void* const* x_peers, const int64_t* rows_peers, int n_peers,
+                         int self_rank, const void* w, const t2sc_epilogue* ep, void* y, int dtype, int Ci, int Co);
+
+/* t2sc_subm_conv_peers over one part of a plan, reading the entries of `peer_nbr` [n_rows,27] (the (owner, row) form
+ * of the map the plan was made for; NULL = the plan's own map) instead of the plan's map.  With a split plan made over the
+ * local map: t2sc_subm_conv_part(INTERIOR) on the local map, then this call with T2SC_PART_BOUNDARY, so that only the
+ * boundary tiles pay for the peer-memory gather. */
+int t2sc_subm_conv_peers_part(t2sc_ctx* ctx, t2sc_plan* plan, const uint32_t* peer_nbr, const void* const* x_peers,
+                              const int64_t* rows_peers, int n_peers, int self_rank, const void* w, const t2sc_epilogue* ep,
+                              void* y, int dtype, int Ci, int Co, int part);
+
+/* Barrier between the ranks of one node through flags in peer-mapped memory, enqueued on the context's stream (no
+ * counterpart in the reference).  flags_peers[r] is rank r's flag array (int32, at least n_peers entries, zero before the
+ * first use) mapped into this process.  The kernel stores `epoch` into entry self_rank of every rank's array (plain
+ * peer stores, release at system scope) and then waits until all entries of its own array have reached `epoch`
+ * (epochs must grow by one per call, starting at 1).  The wait is bounded: after timeout_ms it gives up, sets the
+ * context's status word (t2sc_device_status -> T2SC_ERR_DEVICE) and the kernel returns, so a peer that has died
+ * leaves this GPU usable.  At most 8 ranks. */
+int t2sc_peer_barrier(t2sc_ctx* ctx, void* const* flags_peers, int n_peers, int self_rank, int epoch, int timeout_ms);
 
 /* Replaces layer_norm + act_ + add_ (src/ops.cu:17-113) as one pass over [n,C]; any of the three may
  * be disabled (ln = 0, act = 0, residual = NULL).  In place when y == x. */

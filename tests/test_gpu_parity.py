@@ -183,6 +183,26 @@ def test_fused_epilogues(sp, variant, dt):
     cache.ctx.device_status()
 
 
+@pytest.mark.parametrize("Co", [96, 160, 192, 224])
+def test_layernorm_with_a_width_that_is_no_accumulator_width(sp, Co):
+    """Co = 96 / 160 / 192 / 224 run the tcgen05 conv in 32- or 64-column slabs, so no accumulator holds a whole row:
+    LayerNorm -> activation -> residual must take the row pass instead of being refused."""
+    rng = np.random.default_rng(Co)
+    dt, td = "bf16", torch.bfloat16
+    c, x, w, b = conv_case(rng, 700, 10, 64, Co, dt)
+    g = (1.0 + 0.1 * rng.standard_normal(Co)).astype(np.float32)
+    be = (0.1 * rng.standard_normal(Co)).astype(np.float32)
+    r = rounded(rng.standard_normal((700, Co)), dt)
+    cache = sp.build_neighbors(dev(c))
+    y0 = host(sp.subm_conv(dev(x, td), dev(w, td), dev(b, td), cache, variant="umma"))
+    check_feats(y0, oracle.conv_block(x, w, b, oracle.build_neighbors(c)[0], dt), f"Co={Co} conv")
+    y = sp.subm_conv(dev(x, td), dev(w, td), dev(b, td), cache, ln=(dev(g), dev(be), 1e-6), act="gelu", residual=dev(r, td), variant="umma")
+    cache.ctx.device_status()
+    forced = oracle.round_to(oracle.act(oracle.round_to(oracle.layer_norm(y0, g, be, 1e-6), dt), "gelu"), dt)
+    forced = oracle.round_to(oracle.add(forced, r), dt)
+    check_feats(host(y), forced, f"Co={Co} LayerNorm + GELU + residual on the library's conv output", dt)
+
+
 def test_fused_layernorm_wide_falls_back_to_row_pass(sp):
     rng = np.random.default_rng(12)
     c, x, w, b = conv_case(rng, 600, 9, 64, 512, "bf16")
@@ -244,13 +264,16 @@ def test_subdivision_conv_and_up_tail(sp, variant, dt):
     parent.ctx.device_status()
 
 
-def test_row_ops(sp):
+@pytest.mark.parametrize("C", [96, 100, 512, 1024, 2048, 4096])
+def test_row_ops(sp, C):
+    """LayerNorm / activations / add over rows of 96 .. 4096 channels: the register-resident 16-byte form (C % 8 == 0, up
+    to 2048 channels) and the scalar form (C = 100, C = 4096) against the oracle."""
     rng = np.random.default_rng(31)
     for dt in ("f32", "f16", "bf16"):
-        x = rounded(rng.standard_normal((257, 96)) * 2 + 0.5, dt)
-        r = rounded(rng.standard_normal((257, 96)), dt)
-        g = rng.standard_normal(96).astype(np.float32)
-        b = rng.standard_normal(96).astype(np.float32)
+        x = rounded(rng.standard_normal((257, C)) * 2 + 0.5, dt)
+        r = rounded(rng.standard_normal((257, C)), dt)
+        g = rng.standard_normal(C).astype(np.float32)
+        b = rng.standard_normal(C).astype(np.float32)
         want = oracle.round_to(oracle.layer_norm(x, g, b, 1e-5), dt)
         got = host(sp.layer_norm(dev(x, TD[dt]), dev(g), dev(b), 1e-5))
         check_feats(got, want, f"layer_norm {dt}", dt)
@@ -282,6 +305,119 @@ def test_errors_are_reported_not_thrown_across_the_abi(sp):
         sp.subm_conv(torch.zeros((49, 64), device="cuda", dtype=torch.float16), torch.zeros((64, 27, 64), device="cuda", dtype=torch.float16), None, cache)
     with pytest.raises(sp.T2scError, match="tcgen05"):
         sp.subm_conv(torch.zeros((50, 64), device="cuda"), torch.zeros((64, 27, 64), device="cuda"), None, cache, variant="umma")
+
+
+def test_row_count_is_checked_by_the_library(sp):
+    """The reference requires N == c.N (REQ in src/spconv.cu:162).  Straight through ctypes, past the Python layer's own
+    check: a feature array whose row count is not the plan's is refused with T2SC_ERR_ARG, and a plan that was told
+    about appended halo rows accepts exactly that count."""
+    import ctypes
+    from trellis2_cuda_b200 import _lib
+    c = dev(random_coords(np.random.default_rng(3), 300, 8))
+    cache = sp.build_neighbors(c)
+    plan, ctx, L = cache.plan_for(64, 64), cache.ctx, cache.ctx.lib
+    x = torch.zeros((310, 64), device="cuda", dtype=torch.float16)
+    w = torch.zeros((64, 27, 64), device="cuda", dtype=torch.float16)
+    y = torch.zeros((300, 64), device="cuda", dtype=torch.float16)
+    call = lambda n_in: L.t2sc_subm_conv(ctx.h, plan.h, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(w.data_ptr()), None,
+                                         ctypes.c_void_p(y.data_ptr()), _lib.F16, n_in, 64, 64, 0)
+    assert call(300) == 0
+    for bad in (299, 301, 310, 0):
+        assert call(bad) == -1 and b"rows" in L.t2sc_last_error(ctx.h)
+    assert L.t2sc_plan_set_input_rows(ctx.h, plan.h, 299) == -1          # fewer rows than the map covers
+    assert L.t2sc_plan_set_input_rows(ctx.h, plan.h, 310) == 0
+    assert call(310) == 0 and call(300) == -1
+    assert L.t2sc_plan_set_input_rows(ctx.h, plan.h, 300) == 0
+    ctx.device_status()
+
+
+def test_map_entries_past_the_feature_array_are_reported(sp):
+    """A stale or foreign neighbour map can name rows the feature array does not have.  Both kernel variants read such an
+    entry as an absent neighbour (no access outside x) and t2sc_device_status reports T2SC_ERR_DEVICE; the other
+    rows are computed as usual and the context stays usable."""
+    rng = np.random.default_rng(6)
+    n, C = 600, 64
+    c, x, w, b = conv_case(rng, n, 9, C, C, "bf16")
+    full = sp.build_neighbors(dev(c), want_sorted=False)
+    nbr = full.nbr.clone()
+    bad_rows = torch.tensor([5, 130, 411], device="cuda")
+    nbr[bad_rows, 4] = n + 7                                   # present-looking entries beyond the last row
+    nbr[bad_rows[0], 22] = 0x7FFFFFF0
+    gray = full.gray.clone()
+    gray[bad_rows] |= (1 << 4)
+    gray[bad_rows[0]] |= (1 << 22)
+    ref = host(nbr).astype(np.int64)
+    ref[ref >= n] = -1
+    ref[ref < 0] = oracle.EMPTY
+    want = oracle.conv_block(x, w, b, ref.astype(np.uint32), "bf16")
+    for variant in ("umma", "simt"):
+        cache = sp.cache_from_map(dev(c), nbr.contiguous(), gray.contiguous())
+        y = sp.subm_conv(dev(x, TD["bf16"]), dev(w, TD["bf16"]), dev(b, TD["bf16"]), cache, variant=variant)
+        with pytest.raises(sp.T2scError, match="past the end"):
+            cache.ctx.device_status()
+        check_feats(host(y), want, f"out-of-range entries read as absent ({variant})")
+        cache.ctx.device_status()                              # the status word was cleared by the report
+    good = sp.subm_conv(dev(x, TD["bf16"]), dev(w, TD["bf16"]), dev(b, TD["bf16"]), full)
+    full.ctx.device_status()
+    check_feats(host(good), oracle.conv_block(x, w, b, oracle.build_neighbors(c)[0], "bf16"), "context still usable")
+
+
+def test_add_skip_and_gather_rows_standalone(sp):
+    """k_add_skip / k_gather_rows of the reference (src/sdec.cu:34-43) as stand-alone operators, 8 channels per thread
+    and the scalar form (Co % 8 != 0), against the oracle; fp32 add, one rounding."""
+    rng = np.random.default_rng(9)
+    n, m = 200, 900
+    for dt, Cin, rep in (("bf16", 128, 4), ("f16", 64, 1), ("f32", 32, 2), ("bf16", 32, 3)):
+        Co = (Cin // 8) * rep
+        x = rounded(rng.standard_normal((n, Cin)), dt)
+        h = rounded(rng.standard_normal((m, Co)), dt)
+        src = (rng.integers(0, n, m) * 8 + rng.integers(0, 8, m)).astype(np.int32)
+        want = oracle.round_to(oracle.add_skip(h, x, src, rep), dt)
+        got = sp.add_skip(dev(h, TD[dt]), dev(x, TD[dt]), dev(src), rep)
+        assert np.array_equal(host(got), want), (dt, Cin, rep)
+        if (Cin // 8) * (4 if dt == "f32" else 2) % 16 == 0:
+            g = sp.gather_rows(dev(x, TD[dt]), dev(src), Cin // 8)
+            assert np.array_equal(host(g), oracle.gather_rows(x, src, Cin // 8))
+
+
+def test_a_wait_that_runs_out_returns_an_error_status():
+    """Every mbarrier wait of the tcgen05 kernel is bounded.  The diagnostic build of the library (same sources,
+    -DT2SC_DIAG) can make the weight-loading lane skip the arrival for its first stage and shorten the wait limit: the
+    MMA lane's wait then runs out, every role stops blocking, the kernel drains and returns, and the host reads
+    T2SC_ERR_DEVICE from the status word.  Nothing traps or hangs; the same context then runs a correct conv.  Runs in a
+    process of its own because it loads the diagnostic library instead of the shipped one."""
+    import os, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if not os.path.exists(os.path.join(root, "trellis2_cuda_b200", "libt2sc_diag.so")):
+        pytest.skip("diagnostic build not present (python -m trellis2_cuda_b200.build --diag)")
+    code = r'''
+import os, sys, time
+import numpy as np, torch
+import trellis2_cuda_b200 as sp
+from trellis2_cuda_b200 import scenes, _lib
+assert _lib.LIB_PATH.endswith("libt2sc_diag.so")
+c = torch.from_numpy(scenes.config1_sphere()[:3000]).cuda()
+cache = sp.build_neighbors(c, want_sorted=False)
+x = torch.randn(3000, 64, device="cuda").to(torch.bfloat16)
+w = torch.from_numpy(scenes.kaiming_uniform_weight(64, 64, 1)).cuda().to(torch.bfloat16)
+t0 = time.time()
+y = sp.subm_conv(x, w, None, cache, variant="umma")
+try:
+    cache.ctx.device_status()
+    print("NO_ERROR")
+except sp.T2scError as e:
+    print("STATUS", e.code, "wait gave up" in str(e), round(time.time() - t0, 2))
+cache.ctx.device_status()
+print("CLEARED")
+'''
+    env = dict(os.environ, T2SC_LIBRARY="libt2sc_diag.so", T2SC_DEBUG_SKIP="16", T2SC_WAIT_LIMIT_CYCLES="20000000", PYTHONPATH=root)
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "STATUS -4 True" in r.stdout and "CLEARED" in r.stdout, r.stdout + r.stderr[-2000:]
+    # the same program without the switch: the diagnostic build computes what the shipped library computes
+    env.pop("T2SC_DEBUG_SKIP")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "NO_ERROR" in r.stdout, r.stdout + r.stderr[-2000:]
 
 
 def test_drop_in_for_the_reference_decoder_code(sp):
@@ -387,6 +523,80 @@ def test_sharded_ranks_reproduce_the_single_gpu_conv(sp):
     full.ctx.device_status()
 
 
+@pytest.mark.parametrize("tile_rows", [128, 256])
+def test_split_plan_runs_interior_tiles_before_the_halo_arrives(sp, tile_rows):
+    """Three Morton ranges emulated on one GPU.  A split plan puts the rows that read a halo row into its last tiles.
+    The interior part is run while the halo rows of the local feature array still hold NaN (the exchange has not
+    delivered them): none of its outputs may be touched by them.  The boundary part, run after the halo rows are
+    filled in - from the local array, or gathered from the owners' arrays by the peer-memory kernel - completes the
+    output to the bits of the unsharded conv."""
+    from trellis2_cuda_b200 import sharding
+    c = scenes.config2_shell()[:60000]
+    n, C, world = c.shape[0], 128, 3
+    cd = dev(c)
+    x = torch.randn(n, C, device="cuda").to(torch.bfloat16)
+    w = dev(scenes.kaiming_uniform_weight(C, C, 2), torch.bfloat16)
+    b = torch.randn(C, device="cuda").to(torch.bfloat16)
+    full = sp.build_neighbors(cd, want_sorted=False)
+    want = sp.subm_conv(x, w, b, full, act="silu")
+    starts = sharding.partition(n, world)
+    parts = [x[starts[r]:starts[r + 1]].clone() for r in range(world)]
+    for r in range(world):
+        lo, hi = starts[r], starts[r + 1]
+        nbr_g, gray = sp.build_neighbors_range(cd, lo, hi)
+        halo, nbr_l, _ = sharding.local_map(nbr_g, lo, hi, starts)
+        cache = sp.cache_from_map(cd[lo:hi], nbr_l.contiguous(), gray, tile_rows=tile_rows)
+        plan = cache.split_plan_for(C, C, hi - lo)
+        pt = plan.parts()
+        n_tiles = plan.stats()["tiles"]
+        assert pt["interior_tiles"] + pt["boundary_tiles"] == n_tiles
+        boundary_rows = int((nbr_l >= hi - lo).any(1).sum())
+        assert 0 < pt["boundary_tiles"] <= boundary_rows // tile_rows + 1 and pt["interior_tiles"] > 10 * pt["boundary_tiles"]
+        assert np.array_equal(np.sort(host(plan.order())), np.arange(hi - lo))
+        x_local = torch.cat([x[lo:hi], torch.full((halo.numel(), C), float("nan"), device="cuda", dtype=torch.bfloat16)], 0)
+        y = torch.full((hi - lo, C), 7.0, device="cuda", dtype=torch.bfloat16)
+        sp.subm_conv_split(x_local, w, b, cache, plan, "interior", act="silu", out=y)
+        is_b = (nbr_l >= hi - lo).any(1)
+        assert torch.equal(y[~is_b], want[lo:hi][~is_b])                  # finished, and never saw a halo row
+        assert bool((y[is_b] == 7.0).all())                              # boundary rows are not written by the interior part
+        y2 = y.clone()
+        x_local[hi - lo:] = x[halo]                                       # the exchange delivers
+        sp.subm_conv_split(x_local, w, b, cache, plan, "boundary", act="silu", out=y)
+        assert torch.equal(y, want[lo:hi])
+        # the same boundary tiles through the peer-memory gather, the halo rows still NaN in the local array
+        x_local[hi - lo:] = float("nan")
+        enc = sharding.peer_map(nbr_g, starts).contiguous()
+        ptrs = [p.data_ptr() for p in parts]
+        ptrs[r] = x_local.data_ptr()
+        rows = [p.shape[0] for p in parts]
+        sp.subm_conv_peers(ptrs, rows, r, torch.bfloat16, C, w, b, cache, act="silu", out=y2, plan=plan, part="boundary", peer_nbr=enc)
+        assert torch.equal(y2, want[lo:hi])
+    full.ctx.device_status()
+
+
+def test_peer_barrier_is_bounded(sp):
+    """The flag barrier between ranks, with both "ranks" being flag arrays on this one GPU and their kernels run one
+    after the other.  Rank 1 arrives first: its peer's flag is not set and nothing will set it while the kernel runs,
+    so its wait runs out after the (here short) limit, the kernel returns and the status word reports it - no hang.
+    Rank 0 then finds rank 1's flag and passes; rank 1, called again, passes too."""
+    ctx = sp.context()
+    ctx.device_status()
+    f0 = torch.zeros(8, dtype=torch.int32, device="cuda")
+    f1 = torch.zeros(8, dtype=torch.int32, device="cuda")
+    ptrs = [f0.data_ptr(), f1.data_ptr()]
+    sp.peer_barrier(ctx, ptrs, 1, 1, timeout_ms=50)
+    with pytest.raises(sp.T2scError, match="wait gave up"):
+        ctx.device_status()
+    assert f0.tolist()[:2] == [0, 1] and f1.tolist()[:2] == [0, 1]
+    sp.peer_barrier(ctx, ptrs, 0, 1, timeout_ms=50)
+    ctx.device_status()
+    sp.peer_barrier(ctx, ptrs, 1, 1, timeout_ms=50)
+    ctx.device_status()
+    assert f0.tolist()[:2] == [1, 1] and f1.tolist()[:2] == [1, 1]
+    with pytest.raises(sp.T2scError, match="timeout_ms"):
+        sp.peer_barrier(ctx, ptrs, 0, 2, timeout_ms=0)
+
+
 def test_decoder_like_stack_layer_by_layer(sp):
     """The residual-block stack of configuration 4 (conv -> LN -> GELU -> conv -> residual, then a 2x subdivision
     conv halving the channels) over the first three levels of its voxel pyramid (3,727 -> 16,725 -> 57,120 voxels),
@@ -442,9 +652,11 @@ def test_decoder_like_stack_layer_by_layer(sp):
     cache.ctx.device_status()
 
 
-def test_peer_memory_conv_reproduces_the_single_gpu_conv(sp):
-    """The conv that gathers straight from its peers' arrays (map entries = owner << 29 | row), with the "peers" being
-    three separate arrays on this one GPU: every range must give the bits of the unsharded conv."""
+@pytest.mark.parametrize("world,tile_rows", [(3, 0), (8, 128), (8, 256)])
+def test_peer_memory_conv_reproduces_the_single_gpu_conv(sp, world, tile_rows):
+    """The conv that gathers straight from its peers' arrays (map entries = owner << 28 | row), with the "peers" being
+    separate arrays on this one GPU: every range, owners and self ranks 4..7 included, must give the bits of the
+    unsharded conv, with 128-row and 256-row tiles."""
     from trellis2_cuda_b200 import sharding
     c = scenes.config2_shell()[:50000]
     n, C = c.shape[0], 128
@@ -454,19 +666,25 @@ def test_peer_memory_conv_reproduces_the_single_gpu_conv(sp):
     b = torch.randn(C, device="cuda").to(torch.bfloat16)
     full = sp.build_neighbors(cd, want_sorted=False)
     want = sp.subm_conv(x, w, b, full, act="silu")
-    world = 3
+    assert torch.count_nonzero(want) > 0.9 * want.numel()
     starts = sharding.partition(n, world)
     parts = [x[starts[r]:starts[r + 1]].clone() for r in range(world)]       # one array per "rank"
-    ptrs = [p.data_ptr() for p in parts]
+    ptrs, nrows = [p.data_ptr() for p in parts], [p.shape[0] for p in parts]
     for r in range(world):
         lo, hi = starts[r], starts[r + 1]
         nbr_g, gray = sp.build_neighbors_range(cd, lo, hi)
         enc = sharding.peer_map(nbr_g, starts)
-        assert int(((enc != -1) & ((enc.to(torch.int64) & 0xFFFFFFFF) >> 29 != r)).sum()) > 0      # some rows do come from peers
-        cache = sp.cache_from_map(cd[lo:hi], enc.contiguous(), gray)
-        y = sp.subm_conv_peers(ptrs, r, torch.bfloat16, C, w, b, cache, act="silu")
-        assert torch.equal(y, want[lo:hi])
+        assert int(((enc != -1) & (enc >> sharding.PEER_SHIFT != r)).sum()) > 0      # some rows do come from peers
+        assert bool(((enc >= 0) | (enc == -1)).all())                                   # bit 31 belongs to "absent" alone
+        cache = sp.cache_from_map(cd[lo:hi], enc.contiguous(), gray, tile_rows=tile_rows)
+        y = sp.subm_conv_peers(ptrs, nrows, r, torch.bfloat16, C, w, b, cache, act="silu")
+        assert torch.equal(y, want[lo:hi]), f"rank {r} of {world}"
     full.ctx.device_status()
+    # an entry that names a row its owner does not have is read as absent and reported
+    short = list(nrows); short[world - 1] -= 50
+    sp.subm_conv_peers(ptrs, short, world - 1, torch.bfloat16, C, w, b, cache, act="silu")
+    with pytest.raises(sp.T2scError, match="past the end"):
+        full.ctx.device_status()
 
 
 # ------------------------------------------------------------------------------------------ full-size properties

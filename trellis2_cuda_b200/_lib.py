@@ -6,12 +6,16 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libt2sc.so")
+# T2SC_LIBRARY names another build of the same sources inside this package (the diagnostic build libt2sc_diag.so, which
+# the bounded-wait test loads in a process of its own); the default is the shipped library
+LIB_PATH = os.path.join(HERE, os.path.basename(os.environ.get("T2SC_LIBRARY", "libt2sc.so")))
 
 F32, F16, BF16, U8 = 0, 1, 2, 5
 ACT_NONE, ACT_SILU, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2, 3
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_UMMA, VARIANT_UMMA_PAIR = 0, 1, 2, 3
 STATIC_MAX_ROWS = 65536
+PEER_SHIFT = 28
+PART = {"all": 0, "interior": 1, "boundary": 2}
 
 # every symbol include/t2sc.h declares: (name, restype, argtypes)
 _vp, _i32, _i64, _f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
@@ -42,11 +46,17 @@ SYMBOLS = [
     ("t2sc_gather_rows", _i32, [_vp, _vp, _vp, _i64, _i32, _i32, _vp]),
     ("t2sc_add_skip", _i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32]),
     ("t2sc_plan_create", _i32, [_vp, _vp, _vp, _i64, _vp, _i64, _i64, _i32, _pp]),
+    ("t2sc_plan_create_split", _i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _pp]),
+    ("t2sc_plan_parts", _i32, [_vp, _vp, _pi64, _pi64]),
     ("t2sc_plan_destroy", _i32, [_vp, _vp]),
+    ("t2sc_plan_set_input_rows", _i32, [_vp, _vp, _i64]),
     ("t2sc_plan_stats", _i32, [_vp, _vp, _pi64, _pi64, _pi64]),
     ("t2sc_plan_order", _i32, [_vp, _vp, _vp]),
     ("t2sc_subm_conv", _i32, [_vp, _vp, _vp, _vp, ctypes.POINTER(Epilogue), _vp, _i32, _i64, _i32, _i32, _i32]),
-    ("t2sc_subm_conv_peers", _i32, [_vp, _vp, ctypes.POINTER(ctypes.c_void_p), _i32, _i32, _vp, ctypes.POINTER(Epilogue), _vp, _i32, _i32, _i32]),
+    ("t2sc_subm_conv_part", _i32, [_vp, _vp, _vp, _vp, ctypes.POINTER(Epilogue), _vp, _i32, _i64, _i32, _i32, _i32, _i32]),
+    ("t2sc_subm_conv_peers_part", _i32, [_vp, _vp, _vp, ctypes.POINTER(ctypes.c_void_p), _pi64, _i32, _i32, _vp, ctypes.POINTER(Epilogue), _vp, _i32, _i32, _i32, _i32]),
+    ("t2sc_peer_barrier", _i32, [_vp, ctypes.POINTER(ctypes.c_void_p), _i32, _i32, _i32, _i32]),
+    ("t2sc_subm_conv_peers", _i32, [_vp, _vp, ctypes.POINTER(ctypes.c_void_p), _pi64, _i32, _i32, _vp, ctypes.POINTER(Epilogue), _vp, _i32, _i32, _i32]),
     ("t2sc_row_epilogue", _i32, [_vp, _vp, ctypes.POINTER(Epilogue), _vp, _i64, _i32, _i32]),
     ("t2sc_subm_conv_host", _i32, [_vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32]),
 ]

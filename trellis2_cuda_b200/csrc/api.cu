@@ -1,6 +1,5 @@
 // C-ABI entry points that are not kernels themselves: context, errors, conv dispatch, host-buffer call.
 #include "common.cuh"
-#include <cstdlib>
 
 static char g_create_err[512] = {0};
 
@@ -73,7 +72,10 @@ extern "C" int t2sc_device_status(t2sc_ctx* ctx, int* status_host) {
   T2_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   if (*status_host) {
     T2_CUDA(ctx, cudaMemsetAsync(ctx->status, 0, sizeof(int), ctx->stream));
-    return t2sc_fail(ctx, T2SC_ERR_DEVICE, "a device-side wait gave up (status word 0x%x); results of the last launches are invalid", *status_host);
+    const int waits = *status_host & ~256;        // bits 0..9 bar 8: which role's mbarrier wait, 1024: the peer barrier
+    return t2sc_fail(ctx, T2SC_ERR_DEVICE, "%s%s(status word 0x%x); results of the last launches are invalid",
+                     waits ? "a device-side wait gave up " : "", (*status_host & 256) ? "a neighbour-map entry pointed past the end of its feature array " : "",
+                     *status_host);
   }
   return T2SC_OK;
 }
@@ -81,10 +83,17 @@ extern "C" int t2sc_device_status(t2sc_ctx* ctx, int* status_host) {
 // ------------------------------------------------------------------------------------------ conv dispatch
 extern "C" int t2sc_subm_conv(t2sc_ctx* ctx, t2sc_plan* plan, const void* x, const void* w, const t2sc_epilogue* ep,
                               void* y, int dtype, int64_t n_in, int Ci, int Co, int variant) {
+  return t2sc_subm_conv_part(ctx, plan, x, w, ep, y, dtype, n_in, Ci, Co, variant, T2SC_PART_ALL);
+}
+
+extern "C" int t2sc_subm_conv_part(t2sc_ctx* ctx, t2sc_plan* plan, const void* x, const void* w, const t2sc_epilogue* ep,
+                                   void* y, int dtype, int64_t n_in, int Ci, int Co, int variant, int part) {
   T2_REQ(ctx, ctx && plan, "null context or plan");
+  T2_REQ(ctx, part == T2SC_PART_ALL || part == T2SC_PART_INTERIOR || part == T2SC_PART_BOUNDARY, "part=%d", part);
   T2_REQ(ctx, dtype == T2SC_F32 || dtype == T2SC_F16 || dtype == T2SC_BF16, "dtype %d", dtype);
   T2_REQ(ctx, Ci > 0 && Co > 0 && Ci % 32 == 0, "spconv shapes Ci=%d Co=%d (Ci must be a multiple of 32)", Ci, Co);
-  T2_REQ(ctx, n_in >= 0 && n_in < (1ll << 31), "n_in=%lld", (long long)n_in);
+  // the reference requires N == c.N (src/spconv.cu:162); a plan whose map indexes a longer array says so (t2sc_plan_set_input_rows)
+  T2_REQ(ctx, n_in == plan->n_in, "spconv shapes: x has %lld rows, the plan's neighbour map is over %lld", (long long)n_in, (long long)plan->n_in);
   if (plan->n_out == 0) return T2SC_OK;
   T2_REQ(ctx, x && w && y, "null tensor");
   T2_REQ(ctx, ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((uintptr_t)y % 16 == 0), "x, w, y must be 16-byte aligned");
@@ -96,37 +105,87 @@ extern "C" int t2sc_subm_conv(t2sc_ctx* ctx, t2sc_plan* plan, const void* x, con
   if (variant == T2SC_VARIANT_UMMA && !umma_ok)
     return t2sc_fail(ctx, T2SC_ERR_UNSUPPORTED, "tcgen05 variant needs fp16/bf16, Ci %% 64 == 0, Co %% 32 == 0 (Ci=%d Co=%d dtype=%d)", Ci, Co, dtype);
   bool use_umma = variant == T2SC_VARIANT_UMMA || variant == T2SC_VARIANT_UMMA_PAIR || (variant == T2SC_VARIANT_AUTO && umma_ok);
-  // LayerNorm needs the whole output row in one CTA: fused on the tcgen05 path for Co <= 256, else a second pass
-  bool fuse_all = use_umma && (!e.ln || Co <= 256);
-  static const bool pair_mode = [] { const char* v = getenv("T2SC_CTA_PAIR"); return v && atoi(v) != 0; }();
-  if (variant == T2SC_VARIANT_UMMA_PAIR && !conv_umma2_supported(plan, dtype, Ci, Co, e))
-    return t2sc_fail(ctx, T2SC_ERR_UNSUPPORTED, "two-SM tcgen05 variant needs fp16/bf16, a 256-row plan, Ci %% 64 == 0, Co %% 256 == 0 (Ci=%d Co=%d tile_rows=%d)", Ci, Co, plan->tile_rows);
-  if (variant == T2SC_VARIANT_UMMA_PAIR || (fuse_all && pair_mode && variant != T2SC_VARIANT_SIMT && conv_umma2_supported(plan, dtype, Ci, Co, e)))
-    return conv_umma2_launch(ctx, plan, x, w, w_rows, e, y, dtype, Ci, Co);
-  if (fuse_all) return conv_umma_launch(ctx, plan, x, w, w_rows, e, y, dtype, n_in, Ci, Co);
+  // LayerNorm needs the whole output row in one accumulator: fused on the tcgen05 path when Co is one of its tile widths
+  // (32, 64, 128, 256), else conv + bias first and LayerNorm -> activation -> residual -> skip in a row pass
+  bool fuse_all = use_umma && (!e.ln || conv_umma_fuses_ln(Co));
+  if (variant == T2SC_VARIANT_UMMA_PAIR) {
+    if (!conv_umma2_supported(plan, dtype, Ci, Co, e))
+      return t2sc_fail(ctx, T2SC_ERR_UNSUPPORTED, "two-SM tcgen05 variant needs fp16/bf16, a 256-row plan, Ci %% 64 == 0, Co %% 256 == 0 (Ci=%d Co=%d tile_rows=%d)", Ci, Co, plan->tile_rows);
+    return conv_umma2_launch(ctx, plan, x, w, w_rows, e, y, dtype, n_in, Ci, Co, part);
+  }
+  if (fuse_all) return conv_umma_launch(ctx, plan, x, w, w_rows, e, y, dtype, n_in, Ci, Co, part);
+  // the row pass below runs over all rows: a part of a plan cannot use it
+  T2_REQ(ctx, part == T2SC_PART_ALL || !e.ln, "LayerNorm over Co=%d needs the row pass, which is not available for one part of a plan", Co);
   EpiDev first = e, rest = e;
   if (e.ln) {  // conv + bias now; LN -> act -> residual -> skip in the row pass
     first.ln = 0; first.act = 0; first.residual = nullptr; first.skip_x = nullptr; first.gamma = first.beta = nullptr;
     rest.bias = nullptr;
   }
-  int rc = use_umma ? conv_umma_launch(ctx, plan, x, w, w_rows, first, y, dtype, n_in, Ci, Co)
-                    : conv_simt_launch(ctx, plan, x, w, first, y, dtype, Ci, Co);
+  int rc = use_umma ? conv_umma_launch(ctx, plan, x, w, w_rows, first, y, dtype, n_in, Ci, Co, part)
+                    : conv_simt_launch(ctx, plan, x, w, first, y, dtype, n_in, Ci, Co, part);
   if (rc != T2SC_OK || !e.ln) return rc;
   return row_epilogue_launch(ctx, y, rest, y, plan->n_out, Co, dtype);
 }
 
-extern "C" int t2sc_subm_conv_peers(t2sc_ctx* ctx, t2sc_plan* plan, const void* const* x_peers, int n_peers, int self_rank,
-                                    const void* w, const t2sc_epilogue* ep, void* y, int dtype, int Ci, int Co) {
+extern "C" int t2sc_subm_conv_peers(t2sc_ctx* ctx, t2sc_plan* plan, const void* const* x_peers, const int64_t* rows_peers, int n_peers,
+                                    int self_rank, const void* w, const t2sc_epilogue* ep, void* y, int dtype, int Ci, int Co) {
+  return t2sc_subm_conv_peers_part(ctx, plan, nullptr, x_peers, rows_peers, n_peers, self_rank, w, ep, y, dtype, Ci, Co, T2SC_PART_ALL);
+}
+
+extern "C" int t2sc_subm_conv_peers_part(t2sc_ctx* ctx, t2sc_plan* plan, const uint32_t* peer_nbr, const void* const* x_peers,
+                                         const int64_t* rows_peers, int n_peers, int self_rank, const void* w, const t2sc_epilogue* ep,
+                                         void* y, int dtype, int Ci, int Co, int part) {
   T2_REQ(ctx, ctx && plan, "null context or plan");
-  T2_REQ(ctx, n_peers >= 1 && n_peers <= 8 && x_peers, "n_peers=%d (1..8)", n_peers);
+  T2_REQ(ctx, part == T2SC_PART_ALL || part == T2SC_PART_INTERIOR || part == T2SC_PART_BOUNDARY, "part=%d", part);
+  T2_REQ(ctx, n_peers >= 1 && n_peers <= 8 && x_peers && rows_peers, "n_peers=%d (1..8)", n_peers);
+  for (int r = 0; r < n_peers; r++) T2_REQ(ctx, rows_peers[r] >= 0 && rows_peers[r] <= (1ll << 28), "peer %d has %lld rows (at most 2^28)", r, (long long)rows_peers[r]);
   T2_REQ(ctx, self_rank >= 0 && self_rank < n_peers, "self_rank=%d of %d", self_rank, n_peers);
   if (plan->n_out == 0) return T2SC_OK;
   T2_REQ(ctx, w && y, "null tensor");
   for (int r = 0; r < n_peers; r++) T2_REQ(ctx, x_peers[r] && (uintptr_t)x_peers[r] % 16 == 0, "peer array %d is null or not 16-byte aligned", r);
   EpiDev e = epi_dev(ep);
-  if (!conv_umma_supported(dtype, Ci, Co, e) || (e.ln && Co > 256) || plan->src)
-    return t2sc_fail(ctx, T2SC_ERR_UNSUPPORTED, "peer conv needs a submanifold plan, fp16/bf16, Ci %% 64 == 0, Co %% 32 == 0, LayerNorm only for Co <= 256 (Ci=%d Co=%d dtype=%d)", Ci, Co, dtype);
-  return conv_umma_launch(ctx, plan, x_peers[self_rank], w, Co, e, y, dtype, 0, Ci, Co, x_peers, n_peers, self_rank);
+  if (!conv_umma_supported(dtype, Ci, Co, e) || (e.ln && !conv_umma_fuses_ln(Co)) || plan->src)
+    return t2sc_fail(ctx, T2SC_ERR_UNSUPPORTED, "peer conv needs a submanifold plan, fp16/bf16, Ci %% 64 == 0, Co %% 32 == 0, LayerNorm only for Co in {32,64,128,256} (Ci=%d Co=%d dtype=%d)", Ci, Co, dtype);
+  return conv_umma_launch(ctx, plan, x_peers[self_rank], w, Co, e, y, dtype, rows_peers[self_rank], Ci, Co, part, x_peers, rows_peers, n_peers,
+                          self_rank, peer_nbr);
+}
+
+// ------------------------------------------------------------------------------------------ barrier over peer-mapped flags
+namespace {
+struct FlagPtrs { int* p[8]; };
+// One thread per rank.  Signal: entry `self` of rank t's array.  Wait: entry t of this rank's own array.
+__global__ void k_peer_barrier(FlagPtrs f, int n, int self, int epoch, long long limit_ns, int* status) {
+  const int t = threadIdx.x;
+  if (t >= n) return;
+  __threadfence_system();                 // this GPU's earlier writes are visible to the peers before the flag is
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(f.p[t] + self), "r"(epoch) : "memory");
+  const int* mine = f.p[self] + t;
+  unsigned long long t0, now;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (;;) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if (v - epoch >= 0) break;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    if ((long long)(now - t0) > limit_ns) { atomicOr(status, 1024); break; }     // the peer never arrived: report, do not hang
+    __nanosleep(200);
+  }
+}
+}  // namespace
+
+extern "C" int t2sc_peer_barrier(t2sc_ctx* ctx, void* const* flags_peers, int n_peers, int self_rank, int epoch, int timeout_ms) {
+  T2_REQ(ctx, ctx && flags_peers, "null context or flags");
+  T2_REQ(ctx, n_peers >= 1 && n_peers <= 8 && self_rank >= 0 && self_rank < n_peers, "n_peers=%d self_rank=%d", n_peers, self_rank);
+  T2_REQ(ctx, timeout_ms > 0 && timeout_ms <= 60000, "timeout_ms=%d (1..60000)", timeout_ms);
+  FlagPtrs f;
+  for (int r = 0; r < 8; r++) {
+    f.p[r] = r < n_peers ? (int*)flags_peers[r] : nullptr;
+    if (r < n_peers) T2_REQ(ctx, f.p[r] && (uintptr_t)f.p[r] % 4 == 0, "flag array %d is null or unaligned", r);
+  }
+  T2_CUDA(ctx, cudaSetDevice(ctx->device));
+  k_peer_barrier<<<1, 32, 0, ctx->stream>>>(f, n_peers, self_rank, epoch, (long long)timeout_ms * 1000000ll, ctx->status);
+  T2_LAUNCHED(ctx);
+  return T2SC_OK;
 }
 
 extern "C" int t2sc_row_epilogue(t2sc_ctx* ctx, const void* x, const t2sc_epilogue* ep, void* y, int64_t n, int C, int dtype) {

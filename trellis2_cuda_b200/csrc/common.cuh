@@ -30,11 +30,14 @@ struct PlanTile { int start, rows, wbase; uint32_t mask; };
 struct t2sc_plan {
   i64 n_out = 0;                // output rows
   i64 n_rows = 0;               // rows of nbr / gray
+  i64 n_in = 0;                 // rows of the feature array the map's entries index (n_rows unless t2sc_plan_set_input_rows said more)
   const uint32_t* nbr = nullptr;  // borrowed
   const int32_t* src = nullptr;   // borrowed (NULL for a submanifold plan)
   int32_t* order = nullptr;     // [n_out] output row handled at each plan position
   PlanTile* tiles = nullptr;    // [max_tiles]
-  int* ntiles = nullptr;        // device: realised tile count (<= max_tiles)
+  int* bounds = nullptr;        // device [3]: {0, first boundary tile, realised tile count}; parts are [b0,b1) and [b1,b2)
+  int* ntiles = nullptr;        // = bounds + 2: realised tile count (<= max_tiles)
+  bool split = false;           // made by t2sc_plan_create_split: interior tiles first, boundary tiles last
   unsigned long long* stats = nullptr;  // device [2]: computed taps, active taps
   i64 max_tiles = 0;
   int tile_rows = 256;           // 128 or 256
@@ -62,6 +65,20 @@ template <class T> static inline cudaError_t t2_alloc(t2sc_ctx* ctx, T** p, size
   return cudaMallocAsync((void**)p, (count ? count : 1) * sizeof(T), ctx->stream);
 }
 static inline void t2_free(t2sc_ctx* ctx, void* p) { if (p) cudaFreeAsync(p, ctx->stream); }
+// Scratch of one entry point: everything taken through it goes back to the pool (stream-ordered) when the entry point
+// returns, on the error paths too.
+struct Scratch {
+  t2sc_ctx* ctx; void* held[16]; int n = 0;
+  explicit Scratch(t2sc_ctx* c) : ctx(c) {}
+  Scratch(const Scratch&) = delete;
+  Scratch& operator=(const Scratch&) = delete;
+  template <class T> cudaError_t get(T** p, size_t count) {
+    cudaError_t e = n < 16 ? t2_alloc(ctx, p, count) : cudaErrorMemoryAllocation;
+    if (e == cudaSuccess) held[n++] = (void*)*p;
+    return e;
+  }
+  ~Scratch() { for (int i = 0; i < n; i++) t2_free(ctx, held[i]); }
+};
 
 // ---- storage types: load as float, round float to storage and widen back
 template <class T> __device__ __forceinline__ float to_f(T v);
@@ -102,12 +119,21 @@ static inline EpiDev epi_dev(const t2sc_epilogue* e) {
 }
 
 // implemented in the kernel files
+// which tiles of a plan a launch covers: pointers to the first tile index and to the index one past the last
+struct TilePart { const int* lo; const int* hi; };
+static inline TilePart tile_part(const t2sc_plan* p, int part) {
+  if (part == T2SC_PART_INTERIOR) return TilePart{p->bounds, p->bounds + 1};
+  if (part == T2SC_PART_BOUNDARY) return TilePart{p->bounds + 1, p->bounds + 2};
+  return TilePart{p->bounds, p->bounds + 2};
+}
 int conv_simt_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const void* w, const EpiDev& ep, void* y,
-                     int dtype, int Ci, int Co);
+                     int dtype, i64 n_in, int Ci, int Co, int part = T2SC_PART_ALL);
 bool conv_umma_supported(int dtype, int Ci, int Co, const EpiDev& ep);
+bool conv_umma_fuses_ln(int Co);      // can the tcgen05 path hold a whole output row in one accumulator (fused LayerNorm)?
 int conv_umma_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const void* w, i64 w_rows, const EpiDev& ep, void* y,
-                     int dtype, i64 n_in, int Ci, int Co, const void* const* x_peers = nullptr, int n_peers = 0, int self_rank = 0);
+                     int dtype, i64 n_in, int Ci, int Co, int part = T2SC_PART_ALL, const void* const* x_peers = nullptr,
+                     const int64_t* rows_peers = nullptr, int n_peers = 0, int self_rank = 0, const uint32_t* peer_nbr = nullptr);
 bool conv_umma2_supported(const t2sc_plan* plan, int dtype, int Ci, int Co, const EpiDev& ep);
 int conv_umma2_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const void* w, i64 w_rows, const EpiDev& ep, void* y,
-                      int dtype, int Ci, int Co);
+                      int dtype, i64 n_in, int Ci, int Co, int part = T2SC_PART_ALL);
 int row_epilogue_launch(t2sc_ctx* ctx, const void* x, const EpiDev& ep, void* y, i64 n, int C, int dtype);

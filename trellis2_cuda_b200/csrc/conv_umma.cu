@@ -11,9 +11,9 @@
 //     neighbours, written straight into the 128-byte-swizzled K-major layout tcgen05 reads.  (TMA
 //     tile::gather4 was measured for this job and moves 128-byte rows three times slower.)  Everything that
 //     does not depend on the channel chunk is done once per tap, so a copy is two instructions;
-//   * warp 5 and the last warp feed them neighbour indices through a small ring, one slot per (tile, tap),
-//     each serving half of the tile's rows and running ahead across tile boundaries so that a new tile
-//     starts without a chain of dependent loads;
+//   * warp 5 and the last warp of the base set copy each tile's neighbour-map rows into a [27 taps][rows] table in
+//     shared memory (4-byte cp.async, a whole tile in flight at once), one tile ahead of the gather warps, so
+//     that neither a tap nor a new tile starts with a chain of dependent loads;
 //   * one lane of warp 4 streams the B operand (the tap's [BN x 64] weight slab) with a 3-D TMA tile load
 //     from the weights in their checkpoint layout [Co,27,Ci] - no re-layout, no cluster multicast;
 //   * one lane of warp 6 issues tcgen05.mma (M=128, N=BN, K=16) per half into TMEM and releases smem stages /
@@ -35,12 +35,18 @@ namespace {
 using namespace umma;
 
 // ------------------------------------------------------------------------------------------ kernel
-// Warp roles: 0-3 gather A (cp.async), 4 weights (TMA), 5 and the last warp neighbour-index ring, 6 MMA issue + TMEM
-// owner, 7.. epilogue (4 warps per 128-row half).
+// Warp roles: 0-3 gather A (cp.async), 4 weights (TMA), 5 and the last warp of the base set fill the neighbour-index table,
+// 6 MMA issue + TMEM owner, 7.. epilogue (4 warps per 128-row half).
 // One pipeline stage holds one unit = one (tap, 64-channel chunk).
 // G = gather groups of four warps.  G = 1: the four gather warps fill every unit together.  G = 2 (128-row tiles):
 // a second group of four warps sits behind the epilogue warps and the groups fill alternate units, so one group's
 // barrier round trips and index reads overlap the other group's copies.
+//
+// Neighbour indices reach the gather warps through a per-TILE table in shared memory ([27 taps][rows], two buffers): the
+// two index warps copy the tile's map rows into it with 4-byte cp.async (one 108-byte map row per warp instruction, all
+// rows of the tile in flight at once), mark absent / out-of-range entries, and hand the whole tile over with ONE barrier.
+// (Delivering one tap at a time through a ring made every tap wait for a dependent load of the index warp: with one or
+// two units per tap, at 64 and 128 input channels, that latency was the kernel's time.)
 template <int BN, int MH, int G, bool PEERS, class T>
 __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __grid_constant__ CUtensorMap tmw, const ConvArgs a) {
   static_assert(G == 1 || (G == 2 && MH == 1), "a second gather group only fits beside 128-row tiles");
@@ -50,31 +56,32 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
   constexpr int NB = num_acc_bufs(BN, MH);            // accumulator buffers, each MH halves of BN columns
   constexpr int TMEM_COLS = NB * MH * BN < 32 ? 32 : NB * MH * BN;
   constexpr int ROWS = MH * TILE_M;
+  constexpr int PITCH = tab_pitch(MH), TABW = tab_words(MH);
+  constexpr int NGW = 4 * G;                          // gather warps
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint32_t* ring = (uint32_t*)(smem + S * STAGE);      // IDX_SLOTS x ROWS neighbour indices, one slot per (tile, tap)
-  uint64_t* bars = (uint64_t*)(ring + IDX_SLOTS * ROWS);   // full[S] empty[S] accf[2] acce[2] iready[IDX_SLOTS] ifree[IDX_SLOTS]
-  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * S + 4 + 2 * IDX_SLOTS);
-  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-  const void** peer_base = (const void**)(tmem_slot + 2);      // the peers' array addresses (PEERS only)
-  uint32_t* slot_remote = (uint32_t*)(peer_base + 8);          // PEERS: does the tap in this index slot read any row of a peer?
+  uint32_t* itab = (uint32_t*)(smem + S * STAGE);      // NTAB x [27][PITCH] neighbour indices, one table per tile in flight
+  uint64_t* bars = (uint64_t*)(itab + NTAB * TABW);    // full[S] empty[S] accf[2] acce[2] tready[NTAB] tfree[NTAB]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * S + 4 + 2 * NTAB);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 2);   // [0] a wait gave up, [1] the wait limit
+  const void** peer_base = (const void**)(tmem_slot + 4);      // the peers' array addresses (PEERS only)
+  uint32_t* tab_remote = (uint32_t*)(peer_base + 8);           // PEERS: [NTAB][2 index warps][32 taps] does the tap read any row of a peer?
+  uint32_t* peer_rows = tab_remote + NTAB * 64;                // PEERS: rows of every peer's array (bounds of the map entries)
 
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * S, bar_accf = bar_empty + 8 * S, bar_acce = bar_accf + 16,
-                 bar_iready = bar_acce + 16, bar_ifree = bar_iready + 8 * IDX_SLOTS;
+                 bar_tready = bar_acce + 16, bar_tfree = bar_tready + 8 * NTAB;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nchunk = a.Ci / KCH;
 
   if (threadIdx.x == 0) {
-    const int ngw = (a.dbg_skip & 2048) ? 1 : NUM_PROD_THREADS / 32;       // measurement aid: one gather warp only
-    for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, ngw * 32 + ((a.dbg_skip & 512) ? 0 : 1)); mbar_init(bar_empty + 8 * s, 1); }
+    for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, NUM_PROD_THREADS + 1); mbar_init(bar_empty + 8 * s, 1); }
     for (int b = 0; b < 2; b++) { mbar_init(bar_accf + 8 * b, 1); mbar_init(bar_acce + 8 * b, 128 * MH); }
-    // two index warps fill a slot; with G = 2 every unit of the tap is read by its own group: nchunk reads of 4 warps each
-    for (int r = 0; r < IDX_SLOTS; r++) { mbar_init(bar_iready + 8 * r, 2); mbar_init(bar_ifree + 8 * r, G == 2 ? 4 * nchunk : ngw); }
-    for (int r = 0; r < 2 * IDX_SLOTS; r++) slot_remote[r] = 0;
-    *abort_flag = 0;
-    if (PEERS) for (int r = 0; r < 8; r++) peer_base[r] = a.xp[r];
+    for (int r = 0; r < NTAB; r++) { mbar_init(bar_tready + 8 * r, 2); mbar_init(bar_tfree + 8 * r, NGW); }   // two index warps fill, every gather warp releases
+    for (int r = 0; r < NTAB * 64; r++) tab_remote[r] = 0;
+    abort_flag[0] = 0; abort_flag[1] = a.wait_limit;
+    if (PEERS) for (int r = 0; r < 8; r++) { peer_base[r] = a.xp[r]; peer_rows[r] = a.xp_rows[r]; }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -87,58 +94,76 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int ntiles = *a.ntiles;
+  const int tile0 = *a.tile_lo, ntiles = *a.tile_hi - tile0;
+  const PlanTile* const tiles = a.tiles + tile0;
   const int nitems = ntiles * a.n_cot;
 
-  if (warp < 4 && G == 1) {
-    if ((a.dbg_skip & 2048) && warp > 0) goto role_done;
+  if (warp < 4 || (G == 2 && warp >= warp_group2(MH))) {
     // ===================================================================== A producer: gather rows into the swizzled tile
+    const int g = warp < 4 ? 0 : 1;                                            // gather group (G == 2: fills the units with it % 2 == g)
     const T* x = (const T*)a.x;          // PEERS: the local array, xp[self_rank]
-    const int t = threadIdx.x, jbase = t >> 3, c16 = t & 7;
+    const int t = threadIdx.x & 127, jbase = t >> 3, c16 = t & 7;              // both groups start at a multiple of 128 threads
     const uint32_t dst_thread = (uint32_t)(jbase * 128 + ((c16 ^ (jbase & 7)) << 4));   // (jbase + 16 i) & 7 == jbase & 7
-    uint32_t it = 0, iit = 0;
+    uint32_t it = 0, tt = 0;
     bool alive = true;
-    const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_idx = 0, w_empty = 0, t_role = clock64();
-    PlanTile tile_next = blockIdx.x < nitems ? a.tiles[blockIdx.x / a.n_cot] : PlanTile{};
-    for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+    const bool prof = diag(a, 8); long long w_idx = 0, w_empty = 0, t_role = clock64();
+    PlanTile tile_next = blockIdx.x < nitems ? tiles[blockIdx.x / a.n_cot] : PlanTile{};
+    for (int item = blockIdx.x; item < nitems; item += gridDim.x, tt++) {
       const PlanTile tile = tile_next;
-      if (item + (int)gridDim.x < nitems) tile_next = a.tiles[(item + gridDim.x) / a.n_cot];     // in flight while this tile is gathered
-      for (uint32_t mk = tile.mask; mk; mk &= mk - 1, iit++) {
-        const uint32_t slot = iit % IDX_SLOTS, iph = (iit / IDX_SLOTS) & 1;
-        const bool noring = a.dbg_skip & 128;
-        if (!noring) alive &= mbar_wait_t(bar_iready + 8 * slot, iph, abort_flag, a.status, 32, prof, w_idx);
-        // Ring entries: row number (PEERS: (owner << 29) | row), or RING_ABSENT.  Everything that does not depend on the
-        // channel chunk is done here, once per tap, so that a copy costs two instructions (address, cp.async): the gather
+      if (item + (int)gridDim.x < nitems) tile_next = tiles[(item + gridDim.x) / a.n_cot];     // in flight while this tile is gathered
+      const uint32_t buf = tt % NTAB;
+      // Every gather warp waits for every tile's table, also one that has none of the tile's units (G == 2): a warp can
+      // then never release a buffer twice within one phase of its barrier.
+      alive &= mbar_wait_t(bar_tready + 8 * buf, (tt / NTAB) & 1, abort_flag, a.status, 32, prof, w_idx);
+      const uint32_t* tab = itab + buf * TABW + jbase;
+      for (uint32_t mk = tile.mask; mk;) {
+        const int v = __ffs(mk) - 1;
+        mk &= mk - 1;
+        if (G == 2 && nchunk == 1 && (int)(it & 1) != g) {     // one unit per tap: the other group's tap
+          it++;
+          if (!mk) { __syncwarp(); if (lane == 0 && alive) mbar_arrive(bar_tfree + 8 * buf); }
+          continue;
+        }
+        // Table entries: row number (PEERS: (owner << PEER_SHIFT) | row), or RING_ABSENT.  Everything that does not depend on
+        // the channel chunk is done here, once per tap, so that a copy costs two instructions (address, cp.async): the gather
         // warps run these in order and their instruction count per unit is what bounds narrow layers.
         uint32_t idx[8 * MH], sz[8 * MH];       // rows jbase + 16 i; rows 128.. are the second half, stored right behind the first
 #pragma unroll
-        for (int i = 0; i < 8 * MH; i++) idx[i] = ring[slot * ROWS + jbase + 16 * i];
-        // PEERS: almost every tap reads local rows only (the index warp says so per slot) and takes the plain path with the
+        for (int i = 0; i < 8 * MH; i++) idx[i] = tab[v * PITCH + 16 * i];
+        // PEERS: almost every tap reads local rows only (the index warps say so per tap) and takes the plain path with the
         // owner bits masked off.  For a tap with rows of a peer the addresses are formed here: a table load between the
         // copies below would be ordered after each of them and serialise the loop.
         const T* rp[PEERS ? 8 * MH : 1];
         bool remote = false;
         if constexpr (PEERS) {
-          remote = (slot_remote[2 * slot] | slot_remote[2 * slot + 1]) != 0;
+          remote = (tab_remote[buf * 64 + v] | tab_remote[buf * 64 + 32 + v]) != 0;
           if (__builtin_expect(remote, 0)) {
 #pragma unroll
             for (int i = 0; i < 8 * MH; i++)
-              rp[i] = idx[i] != RING_ABSENT ? (const T*)peer_base[idx[i] >> 29] + (i64)(idx[i] & 0x1FFFFFFFu) * a.Ci + c16 * 8 : x;
+              rp[i] = idx[i] != RING_ABSENT ? (const T*)peer_base[idx[i] >> PEER_SHIFT] + (i64)(idx[i] & PEER_ROW_MASK) * a.Ci + c16 * 8 : x;
           }
         }
 #pragma unroll
         for (int i = 0; i < 8 * MH; i++) {
           sz[i] = (~idx[i] >> 27) & 16u;                                 // 16 bytes, or 0 = zero-fill for an absent neighbour
-          idx[i] &= PEERS ? 0x1FFFFFFFu : 0x7FFFFFFFu;                   // absent -> row 0, a valid address that is not read
+          idx[i] &= PEERS ? PEER_ROW_MASK : 0x7FFFFFFFu;                 // absent -> row 0, a valid address that is not read
         }
-        __syncwarp();
-        if (lane == 0 && !noring) mbar_arrive(bar_ifree + 8 * slot);       // one arrival per gather warp: arrivals on one barrier serialise
+        if (!mk) {        // the tile's last tap is in registers: the index warps may refill this table
+          __syncwarp();
+          if (lane == 0 && alive) mbar_arrive(bar_tfree + 8 * buf);
+        }
         for (int c = 0; c < nchunk; c++, it++) {
+          // G == 2, several units per tap: the groups alternate units.  A group waits on units two apart, never more than the
+          // stage count apart, so it cannot run two phases ahead of a stage, where a parity wait would pass by mistake.
+          if (G == 2 && nchunk > 1 && (int)(it & 1) != g) continue;
           const uint32_t st = it % S;
           alive &= mbar_wait_t(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 1, prof, w_empty);
           const uint32_t dst = smem_base + st * STAGE + dst_thread;
           const T* xs = x + c * KCH + c16 * 8;
-          if (alive && !(a.dbg_skip & 1)) {      // after a wait was given up the ring may hold anything: no more loads
+          // After a wait was given up this thread loads and signals nothing more: the table may hold anything, and an
+          // arrival on a barrier whose phase is still waiting for bytes in flight would overrun its count.
+          if (!alive) continue;
+          if (!diag(a, 1)) {
             if (PEERS && __builtin_expect(remote, 0)) {          // one branch per unit, not per copy: a P2P load when the owner is a peer
 #pragma unroll
               for (int i = 0; i < 8 * MH; i++) cp_async16(dst + i * (16 * 128), rp[i] + c * KCH, sz[i]);
@@ -153,79 +178,26 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
     }
     cp_async_wait_all();
     if (prof && blockIdx.x == 0 && threadIdx.x == 0)
-      printf("[t2sc prof] gather: total %lld clk, wait index ring %lld, wait stage free %lld, units %u\n", clock64() - t_role, w_idx, w_empty, it);
-  } else if (G == 2 && (warp < 4 || warp >= warp_group2(MH))) {
-    // ===================================================================== A producer, two groups filling alternate units
-    const int g = warp < 4 ? 0 : 1;
-    const T* x = (const T*)a.x;
-    const int t = (threadIdx.x & 127), jbase = t >> 3, c16 = t & 7;          // both groups start at a multiple of 128 threads
-    const uint32_t dst_thread = (uint32_t)(jbase * 128 + ((c16 ^ (jbase & 7)) << 4));
-    uint32_t it = 0, iit = 0;
-    bool alive = true;
-    PlanTile tile_next = blockIdx.x < nitems ? a.tiles[blockIdx.x / a.n_cot] : PlanTile{};
-    for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
-      const PlanTile tile = tile_next;
-      if (item + (int)gridDim.x < nitems) tile_next = a.tiles[(item + gridDim.x) / a.n_cot];
-      for (uint32_t mk = tile.mask; mk; mk &= mk - 1, iit++) {
-        for (int c = 0; c < nchunk; c++, it++) {
-          // A group waits on units two apart, never more than the stage count apart: it cannot run two phases ahead of a
-          // stage, where a parity wait would pass by mistake.  (Alternating whole taps breaks exactly that.)
-          if ((int)(it & 1) != g) continue;
-          const uint32_t slot = iit % IDX_SLOTS, iph = (iit / IDX_SLOTS) & 1, st = it % S;
-          alive &= mbar_wait(bar_iready + 8 * slot, iph, abort_flag, a.status, 32);
-          uint32_t idx[8], sz[8];
-#pragma unroll
-          for (int i = 0; i < 8; i++) idx[i] = ring[slot * ROWS + jbase + 16 * i];
-          const T* rp[PEERS ? 8 : 1];
-          bool remote = false;
-          if constexpr (PEERS) {
-            remote = (slot_remote[2 * slot] | slot_remote[2 * slot + 1]) != 0;
-            if (__builtin_expect(remote, 0)) {
-#pragma unroll
-              for (int i = 0; i < 8; i++)
-                rp[i] = idx[i] != RING_ABSENT ? (const T*)peer_base[idx[i] >> 29] + (i64)(idx[i] & 0x1FFFFFFFu) * a.Ci + c16 * 8 : x;
-            }
-          }
-#pragma unroll
-          for (int i = 0; i < 8; i++) {
-            sz[i] = (~idx[i] >> 27) & 16u;
-            idx[i] &= PEERS ? 0x1FFFFFFFu : 0x7FFFFFFFu;
-          }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_ifree + 8 * slot);
-          alive &= mbar_wait(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 1);
-          const uint32_t dst = smem_base + st * STAGE + dst_thread;
-          const T* xs = x + c * KCH + c16 * 8;
-          if (alive && !(a.dbg_skip & 1)) {
-            if (PEERS && __builtin_expect(remote, 0)) {
-#pragma unroll
-              for (int i = 0; i < 8; i++) cp_async16(dst + i * (16 * 128), rp[i] + c * KCH, sz[i]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 8; i++) cp_async16(dst + i * (16 * 128), xs + (i64)idx[i] * a.Ci, sz[i]);
-            }
-          }
-          cp_async_arrive_noinc(bar_full + 8 * st);
-        }
-      }
-    }
-    cp_async_wait_all();
+      printf("[t2sc prof] gather: total %lld clk, wait index table %lld, wait stage free %lld, units %u\n", clock64() - t_role, w_idx, w_empty, it);
   } else if (warp == WARP_TMA) {
     // ===================================================================== B producer (weights by TMA): one lane does it all
-    if (lane == 0 && !(a.dbg_skip & 512)) {
+    if (lane == 0) {
       uint32_t it = 0;
-      PlanTile tile_next = blockIdx.x < nitems ? a.tiles[blockIdx.x / a.n_cot] : PlanTile{};
-      for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+      bool alive = true;        // false once a wait was given up: nothing more is loaded or signalled
+      PlanTile tile_next = blockIdx.x < nitems ? tiles[blockIdx.x / a.n_cot] : PlanTile{};
+      for (int item = blockIdx.x; item < nitems && alive; item += gridDim.x) {
         const int tile_id = item / a.n_cot, cot = item - tile_id * a.n_cot;
         const PlanTile tile = tile_next;
-        if (item + (int)gridDim.x < nitems) tile_next = a.tiles[(item + gridDim.x) / a.n_cot];
+        if (item + (int)gridDim.x < nitems) tile_next = tiles[(item + gridDim.x) / a.n_cot];
         const int wrow = tile.wbase * a.Co + cot * BN;
-        for (uint32_t mk = tile.mask; mk; mk &= mk - 1) {
+        for (uint32_t mk = tile.mask; mk && alive; mk &= mk - 1) {
           const int v = __ffs(mk) - 1;
           for (int c = 0; c < nchunk; c++, it++) {
             const uint32_t st = it % S;
-            mbar_wait(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 2);
-            if (a.dbg_skip & 2) mbar_arrive(bar_full + 8 * st);
+            alive &= mbar_wait(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 2);
+            if (!alive) break;
+            if (diag(a, 16) && it == 0) continue;        // bounded-wait test: this stage never fills, the MMA lane's wait runs out
+            if (diag(a, 2)) mbar_arrive(bar_full + 8 * st);
             else {
               mbar_arrive_expect_tx(bar_full + 8 * st, B_BYTES);
               tma_load_3d(smem_base + st * STAGE + MH * A_BYTES, &tmw, c * KCH, v, wrow, bar_full + 8 * st);
@@ -236,15 +208,15 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
     }
     __syncwarp();
   } else if (warp == WARP_IDX || warp == warp_idx2(MH)) {
-    // ===================================================================== neighbour indices, one ring slot per (tile, tap)
-    // Two index warps, each serving half of the tile's rows (their per-tap instruction path is as critical as the gather warps').
+    // ===================================================================== neighbour-index table, one per tile
+    // Two index warps, each serving half of the tile's rows, one tile ahead of the gather warps.  Tile descriptors are
+    // fetched two tiles ahead and row numbers one tile ahead, so no dependent load sits on a tile boundary; the map rows
+    // themselves go from global to shared memory by cp.async, a whole half tile in flight at once and no register per entry.
     const int ih = warp == WARP_IDX ? 0 : 1;
-    // Runs ahead of the gather warps across tile boundaries, so a new tile starts without a dependent-load bubble.
-    // The loads of one round of IDX_BATCH taps are all in flight before the previous round is handed over, and the
-    // next tile's row numbers are fetched while this tile's taps are served: the warp is never one load latency per tap.
-    constexpr int NR = ROWS / 64, HROWS = ROWS / 2;
-    uint32_t iit = 0;
-    const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_free = 0, w_load = 0, t_role = clock64();
+    constexpr int HROWS = ROWS / 2, NR = HROWS / 32;
+    uint32_t tt = 0;
+    bool oob = false;         // a present map entry pointed past the end of its feature array: read as absent and reported
+    const bool prof = diag(a, 8); long long w_free = 0, w_load = 0, t_role = clock64();
     auto rows_of = [&](const PlanTile& tl, int* nr) {
 #pragma unroll
       for (int i = 0; i < NR; i++) {
@@ -253,74 +225,76 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
         if (j < tl.rows) { const int r = a.order[tl.start + j]; nr[i] = a.src ? (a.src[r] >> 3) : r; }
       }
     };
-    auto load_round = [&](uint32_t (&val)[IDX_BATCH][NR], uint32_t& mk, const int* nr) {
-#pragma unroll
-      for (int q = 0; q < IDX_BATCH; q++) {
-        if (!mk) break;
-        const int v = __ffs(mk) - 1; mk &= mk - 1;
-#pragma unroll
-        for (int i = 0; i < NR; i++) val[q][i] = (nr[i] < 0 || (a.dbg_skip & 32)) ? NBR_EMPTY : __ldg(a.nbr + (i64)nr[i] * 27 + v);
-      }
-    };
-    auto retire_round = [&](const uint32_t (&val)[IDX_BATCH][NR], uint32_t& mk) {
-#pragma unroll
-      for (int q = 0; q < IDX_BATCH; q++) {
-        if (!mk) break;
-        mk &= mk - 1;
-        const uint32_t slot = iit % IDX_SLOTS, iph = (iit / IDX_SLOTS) & 1;
-        mbar_wait_t(bar_ifree + 8 * slot, iph ^ 1, abort_flag, a.status, 64, prof, w_free);
-        if (prof) { long long t0 = clock64(); volatile uint32_t sink = val[q][0]; (void)sink; w_load += clock64() - t0; }
-#pragma unroll
-        for (int i = 0; i < NR; i++) ring[slot * ROWS + ih * HROWS + lane + 32 * i] = val[q][i] == NBR_EMPTY ? RING_ABSENT : val[q][i];
-        if constexpr (PEERS) {
-          bool rem = false;
-#pragma unroll
-          for (int i = 0; i < NR; i++) rem |= val[q][i] != NBR_EMPTY && (int)(val[q][i] >> 29) != a.self_rank;
-          rem = __any_sync(0xffffffffu, rem);
-          if (lane == 0) slot_remote[2 * slot + ih] = rem;
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_iready + 8 * slot);
-        iit++;
-      }
-    };
-    // tile descriptors are fetched two tiles ahead and row numbers one tile ahead, so no dependent load sits on a tile boundary
-    auto desc_of = [&](int item) { return item < nitems ? a.tiles[item / a.n_cot] : PlanTile{}; };
+    auto desc_of = [&](int item) { return item < nitems ? tiles[item / a.n_cot] : PlanTile{}; };
     int nr[NR], nr_next[NR];
     PlanTile tile_n0 = desc_of(blockIdx.x), tile_n1 = desc_of(blockIdx.x + gridDim.x);
     rows_of(tile_n0, nr);
-    for (int item = blockIdx.x; item < nitems && !(a.dbg_skip & 128); item += gridDim.x) {
-      const PlanTile tile = tile_n0;
+    for (int item = blockIdx.x; item < nitems; item += gridDim.x, tt++) {
       const PlanTile tile_n2 = desc_of(item + 2 * gridDim.x);
       rows_of(tile_n1, nr_next);                               // in flight while this tile is served
-      uint32_t mk_load = tile.mask, mk_ret = tile.mask;
-      uint32_t va[IDX_BATCH][NR], vb[IDX_BATCH][NR];
-      load_round(va, mk_load, nr);
-      while (mk_ret) {
-        load_round(vb, mk_load, nr);
-        retire_round(va, mk_ret);
-        if (!mk_ret) break;
-        load_round(va, mk_load, nr);
-        retire_round(vb, mk_ret);
+      const uint32_t buf = tt % NTAB;
+      // warp-uniform: the fill below is a warp-wide exchange of row numbers, and after a wait was given up nothing more
+      // is written or signalled
+      if (!__all_sync(0xffffffffu, mbar_wait_t(bar_tfree + 8 * buf, ((tt / NTAB) & 1) ^ 1, abort_flag, a.status, 64, prof, w_free))) break;
+      uint32_t* tab = itab + buf * TABW + ih * HROWS;
+      long long t_l0 = prof ? clock64() : 0;
+#pragma unroll
+      for (int i = 0; i < NR; i++) {
+#pragma unroll 8
+        for (int l = 0; l < 32; l++) {
+          const int row = __shfl_sync(0xffffffffu, nr[i], l);            // lane l holds the row; lanes 0..26 copy one tap of it each
+          if (lane < 27) {
+            uint32_t* dst = tab + lane * PITCH + 32 * i + l;
+            if (row >= 0 && !diag(a, 32)) cp_async4(smem_u32(dst), a.nbr + (i64)row * 27 + lane);
+            else *dst = RING_ABSENT;                                       // rows past the end of a short tile
+          }
+        }
       }
+      cp_async_wait_all();
+      __syncwarp();
+      if (prof) w_load += clock64() - t_l0;
+      // Second pass over the landed entries, lane = tap: absent and out-of-range entries become RING_ABSENT (bit 31), and
+      // in the peer-memory form each tap learns whether any of its rows lives on another rank.
+      if (lane < 27) {
+        bool rem = false;
+#pragma unroll 8
+        for (int j = 0; j < HROWS; j++) {
+          const uint32_t e = tab[lane * PITCH + j];
+          if (e == RING_ABSENT) continue;
+          bool bad;
+          if constexpr (!PEERS) bad = e >= a.n_in;                   // NBR_EMPTY is above every row count
+          else {
+            const uint32_t owner = e >> PEER_SHIFT;
+            bad = e == NBR_EMPTY || owner >= (uint32_t)a.npeers || (e & PEER_ROW_MASK) >= peer_rows[owner & 7];
+            rem |= !bad && (int)owner != a.self_rank;
+          }
+          if (bad) { oob |= e != NBR_EMPTY; tab[lane * PITCH + j] = RING_ABSENT; }
+        }
+        if constexpr (PEERS) tab_remote[buf * 64 + ih * 32 + lane] = rem;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tready + 8 * buf);
 #pragma unroll
       for (int i = 0; i < NR; i++) nr[i] = nr_next[i];
       tile_n0 = tile_n1; tile_n1 = tile_n2;
     }
+    if (__any_sync(0xffffffffu, oob) && lane == 0) atomicOr(a.status, 256);
     if (prof && blockIdx.x == 0 && lane == 0 && ih == 0)
-      printf("[t2sc prof] index warp: total %lld clk, wait slot free %lld, wait own loads %lld, slots %u\n", clock64() - t_role, w_free, w_load, iit);
+      printf("[t2sc prof] index warp: total %lld clk, wait table free %lld, map rows in flight %lld, tiles %u\n", clock64() - t_role, w_free, w_load, tt);
   } else if (warp == WARP_MMA) {
     // ===================================================================== MMA issuer: one lane waits, issues and commits
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(BN, a.is_bf16);
       uint32_t it = 0, acc_it = 0;
-      const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_full = 0, w_acc = 0, w_issue = 0, w_commit = 0, t_role = clock64();
-      PlanTile tile_next = blockIdx.x < nitems ? a.tiles[blockIdx.x / a.n_cot] : PlanTile{};
-      for (int item = blockIdx.x; item < nitems; item += gridDim.x, acc_it++) {
+      bool alive = true;        // false once a wait was given up: no more MMAs or commits
+      const bool prof = diag(a, 8); long long w_full = 0, w_acc = 0, w_issue = 0, w_commit = 0, t_role = clock64();
+      PlanTile tile_next = blockIdx.x < nitems ? tiles[blockIdx.x / a.n_cot] : PlanTile{};
+      for (int item = blockIdx.x; item < nitems && alive; item += gridDim.x, acc_it++) {
         const PlanTile tile = tile_next;
-        if (item + (int)gridDim.x < nitems) tile_next = a.tiles[(item + gridDim.x) / a.n_cot];
+        if (item + (int)gridDim.x < nitems) tile_next = tiles[(item + gridDim.x) / a.n_cot];
         const uint32_t buf = acc_it % NB, aph = (acc_it / NB) & 1;
-        if (!(a.dbg_skip & 1024)) mbar_wait_t(bar_acce + 8 * buf, aph ^ 1, abort_flag, a.status, 4, prof, w_acc);
+        alive &= mbar_wait_t(bar_acce + 8 * buf, aph ^ 1, abort_flag, a.status, 4, prof, w_acc);
+        if (!alive) break;
         tc_fence_after();                       // the epilogue's tcgen05.ld of this buffer come before the MMAs that overwrite it
         const uint32_t d_tmem = tmem_base + buf * (MH * BN);
         const int halves = tile.rows > TILE_M ? MH : 1;
@@ -330,9 +304,10 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
           // No tcgen05 fence after this wait (the operands are shared-memory data published by the barrier, not tcgen05
           // results) and no proxy fence either: the copies' completion is delivered through the barrier itself
           // (cp.async.mbarrier.arrive.noinc); a fence.proxy.async here was measured at 3-12 % of the kernel time.
-          mbar_wait_t(bar_full + 8 * s, ph, abort_flag, a.status, 8, prof, w_full);
+          alive &= mbar_wait_t(bar_full + 8 * s, ph, abort_flag, a.status, 8, prof, w_full);
+          if (!alive) break;
           long long ti0 = prof ? clock64() : 0;
-          if (!(a.dbg_skip & 4)) {
+          if (!diag(a, 4)) {
             const uint64_t bd = umma_desc(smem_base + s * STAGE + MH * A_BYTES);
             for (int h = 0; h < halves; h++) {
               const uint64_t ad = umma_desc(smem_base + s * STAGE + h * A_BYTES);
@@ -345,7 +320,7 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
           tc_commit(bar_empty + 8 * s);
           if (prof) { w_issue += ti1 - ti0; w_commit += clock64() - ti1; }
         }
-        if (!(a.dbg_skip & 1024)) tc_commit(bar_accf + 8 * buf);
+        if (alive) tc_commit(bar_accf + 8 * buf);
       }
       if (prof && blockIdx.x == 0)
         printf("[t2sc prof] mma: total %lld clk, wait stage full %lld, wait accumulator free %lld, mma issue %lld, commit %lld, steps %u, tiles %u\n",
@@ -357,22 +332,22 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
     const bool has_skip = a.ep.skip_x != nullptr;
     const int q = warp & 3, half = (warp - WARP_EPI0) >> 2, j = half * TILE_M + q * 32 + lane;
     uint32_t acc_it = 0;
-    const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_accf = 0, t_role = clock64();
-    if (a.dbg_skip & 1024) goto role_done;
-    PlanTile tile_next = blockIdx.x < nitems ? a.tiles[blockIdx.x / a.n_cot] : PlanTile{};
+    const bool prof = diag(a, 8); long long w_accf = 0, t_role = clock64();
+    PlanTile tile_next = blockIdx.x < nitems ? tiles[blockIdx.x / a.n_cot] : PlanTile{};
     for (int item = blockIdx.x; item < nitems; item += gridDim.x, acc_it++) {
       const int tile_id = item / a.n_cot, cot = item - tile_id * a.n_cot;
       const PlanTile tile = tile_next;
-      if (item + (int)gridDim.x < nitems) tile_next = a.tiles[(item + gridDim.x) / a.n_cot];
+      if (item + (int)gridDim.x < nitems) tile_next = tiles[(item + gridDim.x) / a.n_cot];
       const uint32_t buf = acc_it % NB, aph = (acc_it / NB) & 1;
       const int orow = j < tile.rows ? a.order[tile.start + j] : -1;
       const int wcol0 = tile.wbase * a.Co + cot * BN;      // bias index of this item's first column
       int sp = 0, ss = 0;
       if (has_skip && orow >= 0) { int sv = a.ep.skip_src[orow]; sp = sv >> 3; ss = sv & 7; }
-      mbar_wait_t(bar_accf + 8 * buf, aph, abort_flag, a.status, 16, prof, w_accf);
+      // warp-uniform (tcgen05.ld is warp-collective); after a wait was given up nothing more is read or signalled
+      if (!__all_sync(0xffffffffu, mbar_wait_t(bar_accf + 8 * buf, aph, abort_flag, a.status, 16, prof, w_accf))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (MH * BN) + half * BN;
-      if (!(a.dbg_skip & 64)) epilogue_row<BN, T>(a, taddr, orow, cot, wcol0, sp, ss);
+      if (!diag(a, 64)) epilogue_row<BN, T>(a, taddr, orow, cot, wcol0, sp, ss);
       tc_fence_before();
       mbar_arrive(bar_acce + 8 * buf);
     }
@@ -380,10 +355,9 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
       printf("[t2sc prof] epilogue: total %lld clk, wait accumulator full %lld (busy %lld), tiles %u\n", clock64() - t_role, w_accf, clock64() - t_role - w_accf, acc_it);
   }
 
-role_done:
   tc_fence_before();
   __syncthreads();
-  if (*abort_flag) {        // a wait gave up: let copies still in flight land before the smem and TMEM are released
+  if (abort_flag[0]) {        // a wait gave up: let copies still in flight land before the smem and TMEM are released
     long long t0 = clock64();
     while (clock64() - t0 < 2000000ll) {}
     __syncthreads();
@@ -423,14 +397,12 @@ int launch_p(t2sc_ctx* ctx, const CUtensorMap& tm, const ConvArgs& args, i64 max
 }
 
 // Gather groups: two for 64 input channels on 128-row tiles (one unit per tap: measured 16-19 % faster; equal at 128
-// channels, 3 % slower at 256), else one.  T2SC_GATHER_GROUPS=1|2 overrides; the peer-memory form has one group.
+// channels, 3 % slower at 256), else one.  The peer-memory form has one group.
 template <int BN, int MH, class T>
 int launch_bn(t2sc_ctx* ctx, const CUtensorMap& tm, const ConvArgs& args, i64 max_items) {
-  static const int force_g = [] { const char* e = getenv("T2SC_GATHER_GROUPS"); return e ? atoi(e) : 0; }();
   if (args.npeers > 0) return launch_p<BN, MH, 1, true, T>(ctx, tm, args, max_items);
   if constexpr (MH == 1) {
-    const int g = force_g ? force_g : (args.Ci == KCH ? 2 : 1);
-    if (g == 2) return launch_p<BN, MH, 2, false, T>(ctx, tm, args, max_items);
+    if (args.Ci == KCH) return launch_p<BN, MH, 2, false, T>(ctx, tm, args, max_items);
   }
   return launch_p<BN, MH, 1, false, T>(ctx, tm, args, max_items);
 }
@@ -457,8 +429,11 @@ bool conv_umma_supported(int dtype, int Ci, int Co, const EpiDev& ep) {
   return (dtype == T2SC_F16 || dtype == T2SC_BF16) && Ci % KCH == 0 && Co % 32 == 0;
 }
 
+bool conv_umma_fuses_ln(int Co) { return pick_bn(Co) == Co; }
+
 int conv_umma_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const void* w, i64 w_rows, const EpiDev& ep, void* y,
-                     int dtype, i64 n_in, int Ci, int Co, const void* const* x_peers, int n_peers, int self_rank) {
+                     int dtype, i64 n_in, int Ci, int Co, int part, const void* const* x_peers, const int64_t* rows_peers, int n_peers,
+                     int self_rank, const uint32_t* peer_nbr) {
   T2_CUDA(ctx, cudaSetDevice(ctx->device));
   const int BN = pick_bn(Co);
   T2_REQ(ctx, BN > 0, "Co=%d", Co);
@@ -476,13 +451,12 @@ int conv_umma_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const 
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (cr != CUDA_SUCCESS) return t2sc_fail(ctx, T2SC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for weights [%lld,27,%d]", (int)cr, (long long)w_rows, Ci);
   ConvArgs args;
-  (void)n_in;
-  static const int dbg_skip = [] { const char* e = getenv("T2SC_DEBUG_SKIP"); return e ? atoi(e) : 0; }();
-  args.dbg_skip = dbg_skip | ((dbg_skip & (128 | 512 | 1024 | 2048)) ? (1 | 2 | 4 | 32 | 64) : 0);   // handshake experiments never touch data
+  diag_args(args);
+  args.n_in = (uint32_t)n_in;
   args.npeers = n_peers; args.self_rank = self_rank;
-  for (int r = 0; r < 8; r++) args.xp[r] = r < n_peers ? x_peers[r] : nullptr;
-  args.x = x; args.y = y; args.nbr = plan->nbr; args.order = plan->order; args.src = plan->src;
-  args.tiles = plan->tiles; args.ntiles = plan->ntiles; args.status = ctx->status;
+  for (int r = 0; r < 8; r++) { args.xp[r] = r < n_peers ? x_peers[r] : nullptr; args.xp_rows[r] = r < n_peers ? (uint32_t)rows_peers[r] : 0u; }
+  args.x = x; args.y = y; args.nbr = peer_nbr ? peer_nbr : plan->nbr; args.order = plan->order; args.src = plan->src;
+  args.tiles = plan->tiles; args.tile_lo = tile_part(plan, part).lo; args.tile_hi = tile_part(plan, part).hi; args.status = ctx->status;
   args.Ci = Ci; args.Co = Co; args.n_cot = Co / BN; args.is_bf16 = dtype == T2SC_BF16; args.ep = ep;
   i64 max_items = plan->max_tiles * args.n_cot;
   if (plan->tile_rows == 2 * TILE_M)

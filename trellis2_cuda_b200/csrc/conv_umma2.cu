@@ -38,12 +38,13 @@ __device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) 
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ void mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-  if (mbar_try_cluster(bar, parity)) return;
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if (mbar_try_cluster(bar, parity)) return true;
   long long t0 = clock64();
   while (!mbar_try_cluster(bar, parity)) {
-    if (*abort_flag || clock64() - t0 > WAIT_LIMIT_CYCLES) { *abort_flag = 1; atomicOr(status, code); return; }
+    if (abort_flag[0] || clock64() - t0 > ((long long)abort_flag[1] << WAIT_LIMIT_SHIFT)) { abort_flag[0] = 1; atomicOr(status, code); return false; }
   }
+  return true;
 }
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -83,7 +84,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) k_conv_umma2(const __grid_consta
     for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, NUM_PROD_THREADS + 1 + (leader ? 1 : 0)); mbar_init(bar_empty + 8 * s, 1); mbar_init(bar_pfull + 8 * s, 1); }
     for (int b = 0; b < 2; b++) { mbar_init(bar_accf + 8 * b, 1); mbar_init(bar_acce + 8 * b, 256); }   // both CTAs' epilogue threads
     for (int r = 0; r < IDX_SLOTS; r++) { mbar_init(bar_iready + 8 * r, 1); mbar_init(bar_ifree + 8 * r, NUM_PROD_THREADS / 32); }
-    *abort_flag = 0;
+    abort_flag[0] = 0; abort_flag[1] = a.wait_limit;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -97,7 +98,8 @@ __global__ void __launch_bounds__(P_THREADS, 1) k_conv_umma2(const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int ntiles = *a.ntiles;
+  const int tile0 = *a.tile_lo, ntiles = *a.tile_hi - tile0;
+  const PlanTile* const tiles = a.tiles + tile0;
   const int nitems = ntiles * a.n_cot;
   const int nchunk = a.Ci / KCH;
   const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
@@ -110,9 +112,9 @@ __global__ void __launch_bounds__(P_THREADS, 1) k_conv_umma2(const __grid_consta
     const uint32_t dst_thread = (uint32_t)(jbase * 128 + ((c16 ^ (jbase & 7)) << 4));
     uint32_t it = 0, iit = 0;
     bool alive = true;        // false once a wait was given up: the index ring may then hold anything, so no more loads
-    const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_empty = 0, w_idx = 0, t_role = clock64();
+    const bool prof = diag(a, 8); long long w_empty = 0, w_idx = 0, t_role = clock64();
     for (int item = pair; item < nitems; item += npairs) {
-      const PlanTile tile = a.tiles[item / a.n_cot];
+      const PlanTile tile = tiles[item / a.n_cot];
       for (uint32_t mk = tile.mask; mk; mk &= mk - 1, iit++) {
         const uint32_t slot = iit % IDX_SLOTS, iph = (iit / IDX_SLOTS) & 1;
         { long long t0 = clock64(); alive &= mbar_wait(bar_iready + 8 * slot, iph, abort_flag, a.status, 32); if (prof) w_idx += clock64() - t0; }
@@ -120,13 +122,14 @@ __global__ void __launch_bounds__(P_THREADS, 1) k_conv_umma2(const __grid_consta
 #pragma unroll
         for (int i = 0; i < 8; i++) idx[i] = ring[slot * TILE_M + jbase + 16 * i];
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_ifree + 8 * slot);       // one arrival per gather warp: arrivals on one barrier serialise
+        if (lane == 0 && alive) mbar_arrive(bar_ifree + 8 * slot);       // one arrival per gather warp: arrivals on one barrier serialise
         for (int c = 0; c < nchunk; c++, it++) {
           const uint32_t s = it % S, ph = (it / S) & 1;
           { long long t0 = clock64(); alive &= mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, a.status, 1); if (prof) w_empty += clock64() - t0; }
           const uint32_t dst = smem_base + s * P_STAGE + dst_thread;
           const T* xs = x + c * KCH + c16 * 8;
-          if (alive && !(a.dbg_skip & 1)) {
+          if (!alive) continue;       // after a wait was given up: no more loads, no more arrivals
+          if (!diag(a, 1)) {
 #pragma unroll
             for (int i = 0; i < 8; i++) {
               const bool present = idx[i] != NBR_EMPTY;
@@ -145,15 +148,15 @@ __global__ void __launch_bounds__(P_THREADS, 1) k_conv_umma2(const __grid_consta
     uint32_t it = 0;
     for (int item = pair; item < nitems; item += npairs) {
       const int tile_id = item / a.n_cot, cot = item - tile_id * a.n_cot;
-      const PlanTile tile = a.tiles[tile_id];
+      const PlanTile tile = tiles[tile_id];
       const int wrow = tile.wbase * a.Co + cot * P_BN + rank * (P_BN / 2);
       for (uint32_t mk = tile.mask; mk; mk &= mk - 1) {
         const int v = __ffs(mk) - 1;
         for (int c = 0; c < nchunk; c++, it++) {
           const uint32_t s = it % S, ph = (it / S) & 1;
-          mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, a.status, 2);
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, a.status, 2))) goto tma_done;
           if (lane == 0) {
-            if (a.dbg_skip & 2) mbar_arrive(bar_full + 8 * s);
+            if (diag(a, 2)) mbar_arrive(bar_full + 8 * s);
             else {
               mbar_arrive_expect_tx(bar_full + 8 * s, P_BHALF);
               tma_load_3d(smem_base + s * P_STAGE + A_BYTES, &tmw, c * KCH, v, wrow, bar_full + 8 * s);
@@ -163,11 +166,13 @@ __global__ void __launch_bounds__(P_THREADS, 1) k_conv_umma2(const __grid_consta
         }
       }
     }
+  tma_done:;
   } else if (warp == P_WARP_IDX) {
     // ===================================================================== neighbour indices of this CTA's rows
     uint32_t iit = 0;
+    bool oob = false;         // a present map entry at or past the end of x: read as absent and reported
     for (int item = pair; item < nitems; item += npairs) {
-      const PlanTile tile = a.tiles[item / a.n_cot];
+      const PlanTile tile = tiles[item / a.n_cot];
       int nr[4];
 #pragma unroll
       for (int i = 0; i < 4; i++) {
@@ -181,24 +186,29 @@ __global__ void __launch_bounds__(P_THREADS, 1) k_conv_umma2(const __grid_consta
         uint32_t val[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) val[i] = nr[i] < 0 ? NBR_EMPTY : __ldg(a.nbr + (i64)nr[i] * 27 + v);
-        mbar_wait(bar_ifree + 8 * slot, iph ^ 1, abort_flag, a.status, 64);
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_ifree + 8 * slot, iph ^ 1, abort_flag, a.status, 64))) goto idx_done;
 #pragma unroll
-        for (int i = 0; i < 4; i++) ring[slot * TILE_M + lane + 32 * i] = val[i];
+        for (int i = 0; i < 4; i++) {
+          oob |= val[i] + 1u > a.n_in;                    // NBR_EMPTY + 1 wraps to 0
+          ring[slot * TILE_M + lane + 32 * i] = val[i] >= a.n_in ? NBR_EMPTY : val[i];
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_iready + 8 * slot);
       }
     }
+  idx_done:
+    if (__any_sync(0xffffffffu, oob) && lane == 0) atomicOr(a.status, 256);
   } else if (warp == P_WARP_RELAY) {
     // ===================================================================== peer: tell the leader that a stage has landed here
     if (leader) {
       // leader: one commit per stage lands on bar_pfull; pass it on as "stage free" to the producers of both CTAs
       uint32_t it = 0;
       for (int item = pair; item < nitems; item += npairs) {
-        const PlanTile tile = a.tiles[item / a.n_cot];
+        const PlanTile tile = tiles[item / a.n_cot];
         const int ksteps = __popc(tile.mask) * nchunk;
         for (int k = 0; k < ksteps; k++, it++) {
           const uint32_t s = it % S, ph = (it / S) & 1;
-          mbar_wait(bar_pfull + 8 * s, ph, abort_flag, a.status, 512);
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_pfull + 8 * s, ph, abort_flag, a.status, 512))) goto relay_done;
           if (lane == 0) {
             mbar_arrive(bar_empty + 8 * s);
             asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(mapa(bar_empty + 8 * s, 1)) : "memory");
@@ -208,13 +218,14 @@ __global__ void __launch_bounds__(P_THREADS, 1) k_conv_umma2(const __grid_consta
       }
     } else {
       uint32_t it = 0;
-      const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_f = 0, t_role = clock64();
+      const bool prof = diag(a, 8); long long w_f = 0, t_role = clock64();
       for (int item = pair; item < nitems; item += npairs) {
-        const PlanTile tile = a.tiles[item / a.n_cot];
+        const PlanTile tile = tiles[item / a.n_cot];
         const int ksteps = __popc(tile.mask) * nchunk;
         for (int k = 0; k < ksteps; k++, it++) {
           const uint32_t s = it % S, ph = (it / S) & 1;
-          { long long t0 = clock64(); mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, 128); if (prof) w_f += clock64() - t0; }
+          { long long t0 = clock64(); const bool ok = __all_sync(0xffffffffu, mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, 128)); if (prof) w_f += clock64() - t0;
+            if (!ok) goto relay_done; }
           // relaxed: the leader never reads this CTA's shared memory with loads; with cta_group::2 each SM's tensor core
           // reads its own shared memory, so only the timing has to cross (a release at cluster scope costs ~900 clk here)
           if (lane == 0) asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(mapa(bar_full + 8 * s, 0)) : "memory");
@@ -223,27 +234,30 @@ __global__ void __launch_bounds__(P_THREADS, 1) k_conv_umma2(const __grid_consta
       }
       if (prof && blockIdx.x == 1 && lane == 0) printf("[t2sc prof pair] relay: total %lld clk, wait local stage %lld, steps %u\n", clock64() - t_role, w_f, it);
     }
+  relay_done:;
   } else if (warp == P_WARP_MMA) {
     // ===================================================================== leader: MMA issue for the pair
     if (leader) {
       const uint32_t idesc = umma_idesc2(a.is_bf16);
       uint32_t it = 0, acc_it = 0;
-      const bool prof = kProfileWaits && (a.dbg_skip & 8); long long w_full = 0, w_pfull = 0, w_acc = 0, t_role = clock64();
+      const bool prof = diag(a, 8); long long w_full = 0, w_pfull = 0, w_acc = 0, t_role = clock64();
       for (int item = pair; item < nitems; item += npairs, acc_it++) {
-        const PlanTile tile = a.tiles[item / a.n_cot];
+        const PlanTile tile = tiles[item / a.n_cot];
         const uint32_t buf = acc_it & 1, aph = (acc_it >> 1) & 1;
-        { long long t0 = clock64(); mbar_wait_cluster(bar_acce + 8 * buf, aph ^ 1, abort_flag, a.status, 4); if (prof) w_acc += clock64() - t0; }
+        { long long t0 = clock64(); const bool ok = __all_sync(0xffffffffu, mbar_wait_cluster(bar_acce + 8 * buf, aph ^ 1, abort_flag, a.status, 4)); if (prof) w_acc += clock64() - t0;
+          if (!ok) goto mma_done; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * P_BN;
         const int ksteps = __popc(tile.mask) * nchunk;
         for (int k = 0; k < ksteps; k++, it++) {
           const uint32_t s = it % S, ph = (it / S) & 1;
-          { long long t0 = clock64(); mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, 8); if (prof) w_full += clock64() - t0; }
+          { long long t0 = clock64(); const bool ok = __all_sync(0xffffffffu, mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, 8)); if (prof) w_full += clock64() - t0;
+            if (!ok) goto mma_done; }
           tc_fence_after();
           if (lane == 0) {
             const uint64_t ad = umma_desc(smem_base + s * P_STAGE), bd = umma_desc(smem_base + s * P_STAGE + A_BYTES);
 #pragma unroll
-            for (int kk = 0; kk < KCH / 16 && !(a.dbg_skip & 4); kk++) tc_mma2(d_tmem, ad + 2 * kk, bd + 2 * kk, idesc, (k > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 0; kk < KCH / 16 && !diag(a, 4); kk++) tc_mma2(d_tmem, ad + 2 * kk, bd + 2 * kk, idesc, (k > 0 || kk > 0) ? 1u : 0u);
             tc_commit2(bar_pfull + 8 * s);                    // "MMAs of this stage are done": the relay warp frees the stage in both CTAs
           }
           __syncwarp();
@@ -255,6 +269,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) k_conv_umma2(const __grid_consta
         printf("[t2sc prof pair] leader mma: total %lld clk, wait own stage %lld, wait peer stage %lld, wait accumulators %lld, steps %u\n",
                clock64() - t_role, w_full, w_pfull, w_acc, it);
     }
+  mma_done:;
   } else {
     // ===================================================================== epilogue of this CTA's 128 rows
     const bool has_skip = a.ep.skip_x != nullptr;
@@ -263,13 +278,13 @@ __global__ void __launch_bounds__(P_THREADS, 1) k_conv_umma2(const __grid_consta
     uint32_t acc_it = 0;
     for (int item = pair; item < nitems; item += npairs, acc_it++) {
       const int tile_id = item / a.n_cot, cot = item - tile_id * a.n_cot;
-      const PlanTile tile = a.tiles[tile_id];
+      const PlanTile tile = tiles[tile_id];
       const uint32_t buf = acc_it & 1, aph = (acc_it >> 1) & 1;
       const int orow = j < tile.rows ? a.order[tile.start + j] : -1;
       const int wcol0 = tile.wbase * a.Co + cot * P_BN;
       int sp = 0, ss = 0;
       if (has_skip && orow >= 0) { int sv = a.ep.skip_src[orow]; sp = sv >> 3; ss = sv & 7; }
-      mbar_wait_cluster(bar_accf + 8 * buf, aph, abort_flag, a.status, 16);
+      if (!__all_sync(0xffffffffu, mbar_wait_cluster(bar_accf + 8 * buf, aph, abort_flag, a.status, 16))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * P_BN;
       epilogue_row<P_BN, T>(a, taddr, orow, cot, wcol0, sp, ss);
@@ -303,7 +318,7 @@ bool conv_umma2_supported(const t2sc_plan* plan, int dtype, int Ci, int Co, cons
 }
 
 int conv_umma2_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const void* w, i64 w_rows, const EpiDev& ep, void* y,
-                      int dtype, int Ci, int Co) {
+                      int dtype, i64 n_in, int Ci, int Co, int part) {
   T2_CUDA(ctx, cudaSetDevice(ctx->device));
   static EncodeTiledFn2 enc = [] {
     void* p = nullptr; cudaDriverEntryPointQueryResult q;
@@ -322,10 +337,10 @@ int conv_umma2_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const
   if (cr != CUDA_SUCCESS) return t2sc_fail(ctx, T2SC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)cr);
   ConvArgs args;
   args.x = x; args.y = y; args.nbr = plan->nbr; args.order = plan->order; args.src = plan->src;
-  args.tiles = plan->tiles; args.ntiles = plan->ntiles; args.status = ctx->status;
+  args.tiles = plan->tiles; args.tile_lo = tile_part(plan, part).lo; args.tile_hi = tile_part(plan, part).hi; args.status = ctx->status;
   args.Ci = Ci; args.Co = Co; args.n_cot = Co / P_BN; args.is_bf16 = dtype == T2SC_BF16; args.ep = ep; args.npeers = 0;
-  static const int dbg_skip = [] { const char* e = getenv("T2SC_DEBUG_SKIP"); return e ? atoi(e) : 0; }();
-  args.dbg_skip = dbg_skip;
+  diag_args(args);
+  args.n_in = (uint32_t)n_in;
   const i64 max_items = plan->max_tiles * args.n_cot;
   int pairs = (int)(max_items < ctx->num_sms / 2 ? max_items : ctx->num_sms / 2);
   cudaLaunchConfig_t cfg = {};
@@ -343,7 +358,6 @@ int conv_umma2_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const
     if (dtype == T2SC_BF16) T2_CUDA(ctx, cudaOccupancyMaxActiveClusters(&mc, k_conv_umma2<__nv_bfloat16>, &cfg));
     else T2_CUDA(ctx, cudaOccupancyMaxActiveClusters(&mc, k_conv_umma2<__half>, &cfg));
     if (mc < 1) return t2sc_fail(ctx, T2SC_ERR_UNSUPPORTED, "no 2-CTA cluster of the pair kernel fits on this device");
-    if (getenv("T2SC_VERBOSE")) fprintf(stderr, "[t2sc] pair kernel: %d co-resident clusters on %d SMs\n", mc, ctx->num_sms);
   }
   if (pairs > mc) pairs = mc;
   cfg.gridDim = dim3(2 * pairs);

@@ -211,6 +211,33 @@ template <class T> __global__ void k_add_skip(T* __restrict__ h, const T* __rest
   h[i] = from_f<T>(to_f<T>(h[i]) + to_f<T>(x[(i64)p * Cin + s * Cs + c / rep]));
 }
 
+// 8 output channels per thread (16-byte accesses of h for the 16-bit types); Co % 8 == 0
+template <class T> __global__ void k_add_skip8(T* __restrict__ h, const T* __restrict__ x, const int* __restrict__ src, i64 nvec,
+                                               int vpr, int Cin, int rep) {
+  const i64 i = blockIdx.x * (i64)blockDim.x + threadIdx.x;
+  if (i >= nvec) return;
+  const i64 r = nvec < (1ll << 31) ? (i64)((unsigned)i / (unsigned)vpr) : i / vpr;
+  const int c0 = (int)(i - r * vpr) * 8, sv = src[r], Cs = Cin / 8;
+  const T* xs = x + (i64)(sv >> 3) * Cin + (sv & 7) * Cs;
+  T* hp = h + i * 8;
+  T v[8];
+  if constexpr (sizeof(T) == 2) *(uint4*)v = *(const uint4*)hp;
+  else { *(float4*)v = *(const float4*)hp; *((float4*)v + 1) = *((const float4*)hp + 1); }
+#pragma unroll
+  for (int e = 0; e < 8; e++) v[e] = from_f<T>(to_f<T>(v[e]) + to_f<T>(xs[(c0 + e) / rep]));
+  if constexpr (sizeof(T) == 2) *(uint4*)hp = *(const uint4*)v;
+  else { *(float4*)hp = *(const float4*)v; *((float4*)hp + 1) = *((const float4*)v + 1); }
+}
+
+template <class T> void add_skip_pick(cudaStream_t st, void* h, const void* x, const int32_t* src, i64 m, int Co, int Cin, int rep) {
+  if (Co % 8 == 0 && (uintptr_t)h % 16 == 0) {
+    const i64 nvec = m * (Co / 8);
+    k_add_skip8<T><<<cdiv_i(nvec, 256), 256, 0, st>>>((T*)h, (const T*)x, src, nvec, Co / 8, Cin, rep);
+  } else {
+    k_add_skip<T><<<cdiv_i(m * Co, 256), 256, 0, st>>>((T*)h, (const T*)x, src, m, Co, Cin, rep);
+  }
+}
+
 }  // namespace
 
 // ------------------------------------------------------------------------------------------ entry points
@@ -224,30 +251,29 @@ extern "C" int t2sc_build_neighbors(t2sc_ctx* ctx, const int32_t* coords, int64_
   T2_REQ(ctx, W > 0 && H > 0 && D > 0, "grid extent %d %d %d", W, H, D);
   T2_CUDA(ctx, cudaSetDevice(ctx->device));
   uint32_t cap = 1; while (cap < 2u * (uint32_t)n) cap <<= 1;            // src/spconv.cu:40
+  Scratch scratch(ctx);            // returned to the pool on every path out of this function
   int* bin = nullptr;
-  unsigned long long* bkeys = nullptr; BrickVals* bvals = nullptr;
+  char* table = nullptr;           // keys [cap] then brick rows [cap]: one allocation, one memset
   const int Wb = (W + 1) / 2, Hb = (H + 1) / 2, Db = (D + 1) / 2;
-  T2_CUDA(ctx, t2_alloc(ctx, &bkeys, cap));
-  T2_CUDA(ctx, t2_alloc(ctx, &bvals, cap));
-  T2_CUDA(ctx, cudaMemsetAsync(bkeys, 0xff, (size_t)cap * sizeof(unsigned long long), ctx->stream));
-  T2_CUDA(ctx, cudaMemsetAsync(bvals, 0xff, (size_t)cap * sizeof(BrickVals), ctx->stream));
+  const size_t table_bytes = (size_t)cap * (sizeof(unsigned long long) + sizeof(BrickVals));
+  T2_CUDA(ctx, scratch.get(&table, table_bytes));
+  unsigned long long* bkeys = (unsigned long long*)table; BrickVals* bvals = (BrickVals*)(table + (size_t)cap * sizeof(unsigned long long));
+  T2_CUDA(ctx, cudaMemsetAsync(table, 0xff, table_bytes, ctx->stream));
   k_brick_insert<<<cdiv_i(n, 256), 256, 0, ctx->stream>>>((const int4*)coords, (int)n, Wb, Hb, Db, bkeys, bvals, cap - 1);
   T2_LAUNCHED(ctx);
-  if (sorted) T2_CUDA(ctx, t2_alloc(ctx, &bin, (size_t)n));
+  if (sorted) T2_CUDA(ctx, scratch.get(&bin, (size_t)n));
   k_brick_neighbors<<<cdiv_i(n, 32), 256, 0, ctx->stream>>>((const int4*)coords, (int)n, W, H, D, Wb, Hb, Db, bkeys, bvals, cap - 1, nbr, gray, bin);
   T2_LAUNCHED(ctx);
-  t2_free(ctx, bkeys); t2_free(ctx, bvals);
   if (sorted) {
-    int *bs = nullptr, *iota = nullptr; void* tmp = nullptr; size_t tb = 0;
-    T2_CUDA(ctx, t2_alloc(ctx, &bs, (size_t)n));
-    T2_CUDA(ctx, t2_alloc(ctx, &iota, (size_t)n));
+    int *bs = nullptr, *iota = nullptr; char* tmp = nullptr; size_t tb = 0;
+    T2_CUDA(ctx, scratch.get(&bs, (size_t)n));
+    T2_CUDA(ctx, scratch.get(&iota, (size_t)n));
     k_iota<<<cdiv_i(n, 256), 256, 0, ctx->stream>>>(iota, (int)n);
     T2_LAUNCHED(ctx);
     // the key has 27 significant bits; radix sort is stable, so ties keep ascending row order
     T2_CUDA(ctx, cub::DeviceRadixSort::SortPairs(nullptr, tb, bin, bs, iota, sorted, (int)n, 0, 27, ctx->stream));
-    T2_CUDA(ctx, t2_alloc(ctx, (char**)&tmp, tb));
+    T2_CUDA(ctx, scratch.get(&tmp, tb));
     T2_CUDA(ctx, cub::DeviceRadixSort::SortPairs(tmp, tb, bin, bs, iota, sorted, (int)n, 0, 27, ctx->stream));
-    t2_free(ctx, tmp); t2_free(ctx, bs); t2_free(ctx, iota); t2_free(ctx, bin);
   }
   return T2SC_OK;
 }
@@ -261,17 +287,17 @@ extern "C" int t2sc_valid_taps(t2sc_ctx* ctx, const int32_t* gray, const int32_t
   T2_REQ(ctx, gray && sorted && seg && list, "null tensor");
   T2_CUDA(ctx, cudaSetDevice(ctx->device));
   int nb = cdiv_i(n, B1);
-  int* code = nullptr; void* tmp = nullptr; size_t tb = 0;
-  T2_CUDA(ctx, t2_alloc(ctx, &code, (size_t)nb));
+  Scratch scratch(ctx);
+  int* code = nullptr; char* tmp = nullptr; size_t tb = 0;
+  T2_CUDA(ctx, scratch.get(&code, (size_t)nb));
   T2_CUDA(ctx, cudaMemsetAsync(seg, 0, sizeof(int), ctx->stream));
   k_block_or<<<cdiv_i((i64)nb * 32, 256), 256, 0, ctx->stream>>>(gray, sorted, (int)n, B1, nb, code, seg + 1);
   T2_LAUNCHED(ctx);
   T2_CUDA(ctx, cub::DeviceScan::InclusiveSum(nullptr, tb, seg + 1, seg + 1, nb, ctx->stream));
-  T2_CUDA(ctx, t2_alloc(ctx, (char**)&tmp, tb));
+  T2_CUDA(ctx, scratch.get(&tmp, tb));
   T2_CUDA(ctx, cub::DeviceScan::InclusiveSum(tmp, tb, seg + 1, seg + 1, nb, ctx->stream));
   k_block_list<<<cdiv_i(nb, 256), 256, 0, ctx->stream>>>(code, seg, nb, list);
   T2_LAUNCHED(ctx);
-  t2_free(ctx, tmp); t2_free(ctx, code);
   if (total_host) {
     int tot = 0;
     T2_CUDA(ctx, cudaMemcpyAsync(&tot, seg + nb, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
@@ -291,17 +317,17 @@ extern "C" int t2sc_subdivide_count(t2sc_ctx* ctx, const void* sub, int sub_dtyp
   T2_CUDA(ctx, cudaMemsetAsync(off, 0, sizeof(int), ctx->stream));
   if (n == 0) return T2SC_OK;
   T2_REQ(ctx, sub != nullptr, "null sub");
-  int* cnt = nullptr; void* tmp = nullptr; size_t tb = 0;
-  T2_CUDA(ctx, t2_alloc(ctx, &cnt, (size_t)n));
+  Scratch scratch(ctx);
+  int* cnt = nullptr; char* tmp = nullptr; size_t tb = 0;
+  T2_CUDA(ctx, scratch.get(&cnt, (size_t)n));
   int g = cdiv_i(n, 256);
   if (sub_dtype == T2SC_F16) k_c2s_count<__half><<<g, 256, 0, ctx->stream>>>((const __half*)sub, (int)n, cnt);
   else if (sub_dtype == T2SC_BF16) k_c2s_count<__nv_bfloat16><<<g, 256, 0, ctx->stream>>>((const __nv_bfloat16*)sub, (int)n, cnt);
   else k_c2s_count<uint8_t><<<g, 256, 0, ctx->stream>>>((const uint8_t*)sub, (int)n, cnt);
   T2_LAUNCHED(ctx);
   T2_CUDA(ctx, cub::DeviceScan::InclusiveSum(nullptr, tb, cnt, off + 1, (int)n, ctx->stream));
-  T2_CUDA(ctx, t2_alloc(ctx, (char**)&tmp, tb));
+  T2_CUDA(ctx, scratch.get(&tmp, tb));
   T2_CUDA(ctx, cub::DeviceScan::InclusiveSum(tmp, tb, cnt, off + 1, (int)n, ctx->stream));
-  t2_free(ctx, tmp); t2_free(ctx, cnt);
   if (m_host) {
     int m = 0;
     T2_CUDA(ctx, cudaMemcpyAsync(&m, off + n, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
@@ -350,10 +376,9 @@ extern "C" int t2sc_add_skip(t2sc_ctx* ctx, void* h, const void* x, const int32_
   if (m == 0) return T2SC_OK;
   T2_REQ(ctx, h && x && src, "null tensor");
   T2_CUDA(ctx, cudaSetDevice(ctx->device));
-  int g = cdiv_i(m * Co, 256);
-  if (dtype == T2SC_F16) k_add_skip<__half><<<g, 256, 0, ctx->stream>>>((__half*)h, (const __half*)x, src, m, Co, Cin, rep);
-  else if (dtype == T2SC_BF16) k_add_skip<__nv_bfloat16><<<g, 256, 0, ctx->stream>>>((__nv_bfloat16*)h, (const __nv_bfloat16*)x, src, m, Co, Cin, rep);
-  else if (dtype == T2SC_F32) k_add_skip<float><<<g, 256, 0, ctx->stream>>>((float*)h, (const float*)x, src, m, Co, Cin, rep);
+  if (dtype == T2SC_F16) add_skip_pick<__half>(ctx->stream, h, x, src, m, Co, Cin, rep);
+  else if (dtype == T2SC_BF16) add_skip_pick<__nv_bfloat16>(ctx->stream, h, x, src, m, Co, Cin, rep);
+  else if (dtype == T2SC_F32) add_skip_pick<float>(ctx->stream, h, x, src, m, Co, Cin, rep);
   else return t2sc_fail(ctx, T2SC_ERR_ARG, "dtype %d", dtype);
   T2_LAUNCHED(ctx);
   return T2SC_OK;
@@ -373,18 +398,18 @@ extern "C" int t2sc_build_neighbors_range(t2sc_ctx* ctx, const int32_t* coords, 
   T2_REQ(ctx, W > 0 && H > 0 && D > 0, "grid extent %d %d %d", W, H, D);
   T2_CUDA(ctx, cudaSetDevice(ctx->device));
   uint32_t cap = 1; while (cap < 2u * (uint32_t)n) cap <<= 1;
-  unsigned long long* bkeys = nullptr; BrickVals* bvals = nullptr;
+  Scratch scratch(ctx);
+  char* table = nullptr;
   const int Wb = (W + 1) / 2, Hb = (H + 1) / 2, Db = (D + 1) / 2;
-  T2_CUDA(ctx, t2_alloc(ctx, &bkeys, cap));
-  T2_CUDA(ctx, t2_alloc(ctx, &bvals, cap));
-  T2_CUDA(ctx, cudaMemsetAsync(bkeys, 0xff, (size_t)cap * sizeof(unsigned long long), ctx->stream));
-  T2_CUDA(ctx, cudaMemsetAsync(bvals, 0xff, (size_t)cap * sizeof(BrickVals), ctx->stream));
+  const size_t table_bytes = (size_t)cap * (sizeof(unsigned long long) + sizeof(BrickVals));
+  T2_CUDA(ctx, scratch.get(&table, table_bytes));
+  unsigned long long* bkeys = (unsigned long long*)table; BrickVals* bvals = (BrickVals*)(table + (size_t)cap * sizeof(unsigned long long));
+  T2_CUDA(ctx, cudaMemsetAsync(table, 0xff, table_bytes, ctx->stream));
   k_brick_insert<<<cdiv_i(n, 256), 256, 0, ctx->stream>>>((const int4*)coords, (int)n, Wb, Hb, Db, bkeys, bvals, cap - 1);
   T2_LAUNCHED(ctx);
   const i64 m = row_hi - row_lo;
   k_brick_neighbors<<<cdiv_i(m, 32), 256, 0, ctx->stream>>>((const int4*)coords + row_lo, (int)m, W, H, D, Wb, Hb, Db, bkeys, bvals, cap - 1, nbr, gray, nullptr);
   T2_LAUNCHED(ctx);
-  t2_free(ctx, bkeys); t2_free(ctx, bvals);
   return T2SC_OK;
 }
 

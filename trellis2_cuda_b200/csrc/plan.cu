@@ -5,6 +5,9 @@
 // rows, mask key): rows with similar masks still become adjacent, which keeps the union mask of a tile
 // close to its rows' own masks, but only inside a run of caller rows, so the gathers of one tile stay
 // inside a region that fits the L2.  Weight groups are the 8 child slots of a 2x-subdivision conv.
+// A plan made for one rank of a partitioned scene (t2sc_plan_create_split) has two groups of the other kind: rows none
+// of whose taps reads a halo row (interior), and rows that do (boundary), the boundary tiles last, so that the interior
+// tiles can run while the halo rows are still in flight.
 // Everything is built on the device; no host round trip is needed to launch a conv from a plan.
 #include "common.cuh"
 #include <cub/cub.cuh>
@@ -29,20 +32,29 @@ __device__ __forceinline__ uint32_t mask_key(uint32_t g) {
 }
 
 // key = group | block (block_bits wide) | mask key (27 bits), most significant first
-__global__ void k_plan_keys(const int* __restrict__ gray, const int* __restrict__ src, i64 m, i64 block_rows, int block_bits,
+// halo_from > 0 (split plan, no src): group 1 = rows with a map entry >= halo_from (a row of a peer), group 0 = the rest
+__global__ void k_plan_keys(const int* __restrict__ gray, const int* __restrict__ src, const uint32_t* __restrict__ nbr, uint32_t halo_from,
+                            i64 m, i64 block_rows, int block_bits,
                             unsigned long long* __restrict__ keys, int* __restrict__ iota, int* __restrict__ group_cnt) {
   i64 i = blockIdx.x * (i64)blockDim.x + threadIdx.x;
   if (i >= m) return;
   int grp = 0; i64 nrow = i;
   if (src) { int s = src[i]; grp = s & 7; nrow = s >> 3; }
+  else if (halo_from) {
+    const uint32_t* e = nbr + i * 27;
+#pragma unroll 9
+    for (int v = 0; v < 27; v++) { const uint32_t r = __ldg(e + v); grp |= (r != NBR_EMPTY && r >= halo_from) ? 1 : 0; }
+  }
   unsigned long long blk = (unsigned long long)(i / block_rows);
   keys[i] = ((unsigned long long)grp << (27 + block_bits)) | (blk << 27) | mask_key((uint32_t)gray[nrow]);
   iota[i] = (int)i;
-  if (src) atomicAdd(&group_cnt[grp], 1);
+  if (src || halo_from) atomicAdd(&group_cnt[grp], 1);
 }
 
 // one thread: tile offsets of the (up to 8) groups
-__global__ void k_plan_groups(const int* __restrict__ group_cnt, int ngroups, i64 m, int TILE, int* __restrict__ gmeta, int* __restrict__ ntiles) {
+// bounds[0..2] = {0, first boundary tile, number of tiles}: the interior part of a split plan is tiles
+// [bounds[0], bounds[1]), its boundary part [bounds[1], bounds[2]); any other plan is all interior.
+__global__ void k_plan_groups(const int* __restrict__ group_cnt, int ngroups, int split, i64 m, int TILE, int* __restrict__ gmeta, int* __restrict__ bounds) {
   // gmeta[g] = first row of group g, gmeta[16+g] = first tile of group g
   int row = 0, tile = 0;
   for (int g = 0; g < ngroups; g++) {
@@ -51,12 +63,12 @@ __global__ void k_plan_groups(const int* __restrict__ group_cnt, int ngroups, i6
     row += c; tile += (c + TILE - 1) / TILE;
   }
   gmeta[ngroups] = row; gmeta[16 + ngroups] = tile;
-  *ntiles = tile;
+  bounds[0] = 0; bounds[1] = split ? gmeta[16 + 1] : tile; bounds[2] = tile;
 }
 
 // one warp per tile: extent, weight base, OR of the row masks; also the plan's tap statistics
 __global__ void k_plan_tiles(const int* __restrict__ gray, const int* __restrict__ src, const int* __restrict__ order,
-                             const int* __restrict__ gmeta, int ngroups, int TILE, const int* __restrict__ ntiles,
+                             const int* __restrict__ gmeta, int ngroups, int split, int TILE, const int* __restrict__ ntiles,
                              PlanTile* __restrict__ tiles, unsigned long long* __restrict__ stats) {
   int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (t >= *ntiles) return;
@@ -75,7 +87,7 @@ __global__ void k_plan_tiles(const int* __restrict__ gray, const int* __restrict
   act = __reduce_add_sync(0xffffffffu, act);
   if (o == 0) o = 1u << 13;       // no row of the tile has any neighbour: one tap of zero-filled rows still initialises the accumulators
   if (lane == 0) {
-    tiles[t] = PlanTile{start, rows, g, o};      // wbase holds the group; the conv multiplies by Co
+    tiles[t] = PlanTile{start, rows, split ? 0 : g, o};      // wbase holds the child slot (the conv multiplies by Co); the two parts of a split plan share one weight set
     atomicAdd(&stats[0], (unsigned long long)rows * __popc(o));
     atomicAdd(&stats[1], (unsigned long long)act);
   }
@@ -83,8 +95,8 @@ __global__ void k_plan_tiles(const int* __restrict__ gray, const int* __restrict
 
 }  // namespace
 
-extern "C" int t2sc_plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_t* gray, int64_t n_rows,
-                                const int32_t* src, int64_t m, int64_t block_rows, int tile_rows, t2sc_plan** out) {
+static int plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_t* gray, int64_t n_rows,
+                       const int32_t* src, int64_t m, int64_t halo_from, int64_t block_rows, int tile_rows, t2sc_plan** out) {
   T2_REQ(ctx, ctx && out, "null context or out");
   *out = nullptr;
   T2_REQ(ctx, n_rows >= 0 && m >= 0 && m < (1ll << 30) && n_rows < (1ll << 30), "n_rows=%lld m=%lld", (long long)n_rows, (long long)m);
@@ -97,9 +109,11 @@ extern "C" int t2sc_plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_
   const int TILE = tile_rows;
   T2_REQ(ctx, (m + block_rows - 1) / block_rows < (1ll << 23), "block_rows=%lld too small for m=%lld", (long long)block_rows, (long long)m);
   t2sc_plan* p = new t2sc_plan();
-  p->n_out = m; p->n_rows = n_rows; p->nbr = nbr; p->src = src; p->tile_rows = tile_rows;
-  int ngroups = src ? 8 : 1;
-  p->max_tiles = cdiv_i(m, TILE) + (src ? 8 : 0);
+  p->n_out = m; p->n_rows = n_rows; p->n_in = n_rows; p->nbr = nbr; p->src = src; p->tile_rows = tile_rows;
+  const int split = halo_from > 0 ? 1 : 0;
+  p->split = split != 0;
+  int ngroups = src ? 8 : (split ? 2 : 1);
+  p->max_tiles = cdiv_i(m, TILE) + (src ? 8 : (split ? 2 : 0));
   unsigned long long *keys = nullptr, *keys2 = nullptr; int *iota = nullptr, *gcnt = nullptr, *gmeta = nullptr; void* tmp = nullptr;
   auto fail = [&](cudaError_t e) {
     t2_free(ctx, keys); t2_free(ctx, keys2); t2_free(ctx, iota); t2_free(ctx, gcnt); t2_free(ctx, gmeta); t2_free(ctx, tmp);
@@ -110,9 +124,10 @@ extern "C" int t2sc_plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_
 #define PL(call) do { if ((e = (call)) != cudaSuccess) return fail(e); } while (0)
   PL(t2_alloc(ctx, &p->order, (size_t)m));
   PL(t2_alloc(ctx, &p->tiles, (size_t)p->max_tiles));
-  PL(t2_alloc(ctx, &p->ntiles, 1));
+  PL(t2_alloc(ctx, &p->bounds, 3));
+  p->ntiles = p->bounds + 2;
   PL(t2_alloc(ctx, &p->stats, 2));
-  PL(cudaMemsetAsync(p->ntiles, 0, sizeof(int), ctx->stream));
+  PL(cudaMemsetAsync(p->bounds, 0, 3 * sizeof(int), ctx->stream));
   PL(cudaMemsetAsync(p->stats, 0, 2 * sizeof(unsigned long long), ctx->stream));
   if (m > 0) {
     PL(t2_alloc(ctx, &keys, (size_t)m)); PL(t2_alloc(ctx, &keys2, (size_t)m)); PL(t2_alloc(ctx, &iota, (size_t)m));
@@ -120,19 +135,19 @@ extern "C" int t2sc_plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_
     PL(cudaMemsetAsync(gcnt, 0, 8 * sizeof(int), ctx->stream));
     int block_bits = 0;
     while (((m + block_rows - 1) / block_rows) > (1ll << block_bits)) block_bits++;
-    k_plan_keys<<<cdiv_i(m, 256), 256, 0, ctx->stream>>>(gray, src, m, block_rows, block_bits, keys, iota, gcnt);
+    k_plan_keys<<<cdiv_i(m, 256), 256, 0, ctx->stream>>>(gray, src, nbr, (uint32_t)halo_from, m, block_rows, block_bits, keys, iota, gcnt);
     ctx->launches++; PL(cudaGetLastError());
     size_t tb = 0;
-    int end_bit = 27 + block_bits + (src ? 3 : 0);
+    int end_bit = 27 + block_bits + (src ? 3 : (split ? 1 : 0));
     // the 3 least significant key bits (centre tap and two face taps) do not change the tiles' masks measurably
     // (active/computed 0.855 -> 0.853) and leaving them out saves a radix pass on maps sorted as one block
     const int begin_bit = 3;
     PL(cub::DeviceRadixSort::SortPairs(nullptr, tb, keys, keys2, iota, p->order, (int)m, begin_bit, end_bit, ctx->stream));
     PL(t2_alloc(ctx, (char**)&tmp, tb));
     PL(cub::DeviceRadixSort::SortPairs(tmp, tb, keys, keys2, iota, p->order, (int)m, begin_bit, end_bit, ctx->stream));
-    k_plan_groups<<<1, 1, 0, ctx->stream>>>(gcnt, ngroups, m, TILE, gmeta, p->ntiles);
+    k_plan_groups<<<1, 1, 0, ctx->stream>>>(gcnt, ngroups, split, m, TILE, gmeta, p->bounds);
     ctx->launches++; PL(cudaGetLastError());
-    k_plan_tiles<<<cdiv_i(p->max_tiles * 32, 256), 256, 0, ctx->stream>>>(gray, src, p->order, gmeta, ngroups, TILE, p->ntiles, p->tiles, p->stats);
+    k_plan_tiles<<<cdiv_i(p->max_tiles * 32, 256), 256, 0, ctx->stream>>>(gray, src, p->order, gmeta, ngroups, split, TILE, p->ntiles, p->tiles, p->stats);
     ctx->launches++; PL(cudaGetLastError());
   }
 #undef PL
@@ -141,11 +156,40 @@ extern "C" int t2sc_plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_
   return T2SC_OK;
 }
 
+extern "C" int t2sc_plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_t* gray, int64_t n_rows,
+                                const int32_t* src, int64_t m, int64_t block_rows, int tile_rows, t2sc_plan** out) {
+  return plan_create(ctx, nbr, gray, n_rows, src, m, 0, block_rows, tile_rows, out);
+}
+
+extern "C" int t2sc_plan_create_split(t2sc_ctx* ctx, const uint32_t* nbr, const int32_t* gray, int64_t n_rows, int64_t n_own,
+                                      int64_t block_rows, int tile_rows, t2sc_plan** out) {
+  T2_REQ(ctx, ctx != nullptr, "null context");
+  T2_REQ(ctx, n_own > 0 && n_own < (1ll << 31), "n_own=%lld", (long long)n_own);
+  return plan_create(ctx, nbr, gray, n_rows, nullptr, n_rows, n_own, block_rows, tile_rows, out);
+}
+
+extern "C" int t2sc_plan_parts(t2sc_ctx* ctx, t2sc_plan* p, int64_t* interior_tiles, int64_t* boundary_tiles) {
+  T2_REQ(ctx, ctx && p, "null context or plan");
+  int b[3] = {0, 0, 0};
+  T2_CUDA(ctx, cudaMemcpyAsync(b, p->bounds, sizeof(b), cudaMemcpyDeviceToHost, ctx->stream));
+  T2_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (interior_tiles) *interior_tiles = b[1] - b[0];
+  if (boundary_tiles) *boundary_tiles = b[2] - b[1];
+  return T2SC_OK;
+}
+
+extern "C" int t2sc_plan_set_input_rows(t2sc_ctx* ctx, t2sc_plan* p, int64_t n_in) {
+  T2_REQ(ctx, ctx && p, "null context or plan");
+  T2_REQ(ctx, n_in >= p->n_rows && n_in < (1ll << 31), "n_in=%lld for a map over %lld rows", (long long)n_in, (long long)p->n_rows);
+  p->n_in = n_in;
+  return T2SC_OK;
+}
+
 extern "C" int t2sc_plan_destroy(t2sc_ctx* ctx, t2sc_plan* p) {
   if (!p) return T2SC_OK;
   T2_REQ(ctx, ctx != nullptr, "null context");
   cudaSetDevice(ctx->device);
-  t2_free(ctx, p->order); t2_free(ctx, p->tiles); t2_free(ctx, p->ntiles); t2_free(ctx, p->stats);
+  t2_free(ctx, p->order); t2_free(ctx, p->tiles); t2_free(ctx, p->bounds); t2_free(ctx, p->stats);
   delete p;
   return T2SC_OK;
 }

@@ -11,18 +11,24 @@ constexpr int KCH = 64;                      // channels per pipeline step = one
 constexpr int A_BYTES = TILE_M * 128;
 constexpr int NUM_PROD_THREADS = 128;
 constexpr int WARP_TMA = 4, WARP_IDX = 5, WARP_MMA = 6, WARP_EPI0 = 7;
-#ifdef T2SC_PROFILE_WAITS
-constexpr bool kProfileWaits = true;     // diagnostic build (python -m trellis2_cuda_b200.build --profile-waits)
+// Diagnostic build (python -m trellis2_cuda_b200.build --diag -> libt2sc_diag.so): measurement switches that disable
+// parts of the kernel, per-role wait timers and a settable wait limit.  None of it exists in the shipped library:
+// kDiag is a compile-time false there and every test on it folds away.
+#ifdef T2SC_DIAG
+constexpr bool kDiag = true;
 #else
-constexpr bool kProfileWaits = false;
+constexpr bool kDiag = false;
 #endif
-constexpr int IDX_SLOTS = 8;
-constexpr uint32_t RING_ABSENT = 0x80000000u;      // index-ring entry of an absent neighbour (row numbers are below 2^30)
-#ifndef T2SC_IDX_BATCH
-#define T2SC_IDX_BATCH 1      // measured: 1 is as fast as 2 or 4 with 128-row tiles and faster with 256-row tiles
-#endif
-constexpr int IDX_BATCH = T2SC_IDX_BATCH;          // taps whose index loads are issued together by the index warp
+constexpr bool kProfileWaits = kDiag;
+constexpr int IDX_SLOTS = 8;                       // index ring of the two-SM kernel: one slot per (tile, tap)
+constexpr int NTAB = 2;                            // neighbour-index tables of the single-CTA kernel: one per tile in flight
+constexpr uint32_t RING_ABSENT = 0x80000000u;      // index entry of an absent neighbour (row numbers are below 2^30)
+// Peer-memory form: a present map entry is (owner << PEER_SHIFT) | row with owner < 8 and row < 2^28, so bit 31 stays
+// free for RING_ABSENT whatever the owner.
+constexpr int PEER_SHIFT = 28;
+constexpr uint32_t PEER_ROW_MASK = (1u << PEER_SHIFT) - 1;
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // ~2 s at boost clock
+constexpr int WAIT_LIMIT_SHIFT = 10;                    // the limit travels to the kernel in units of 1024 cycles
 constexpr int SMEM_BUDGET = 227 * 1024;
 
 // warps: 4 gather, weights, indices, MMA, 4 per 128-row half for the epilogue, a second index warp (each serves half the
@@ -31,7 +37,11 @@ __host__ __device__ constexpr int num_threads(int MH, int G = 1) { return (8 + 4
 __host__ __device__ constexpr int warp_idx2(int MH) { return 7 + 4 * MH; }
 __host__ __device__ constexpr int warp_group2(int MH) { return 8 + 4 * MH; }
 __host__ __device__ constexpr int stage_bytes(int BN, int MH) { return MH * A_BYTES + BN * 128; }
-__host__ __device__ constexpr int aux_bytes(int MH) { return IDX_SLOTS * MH * TILE_M * 4 + 512; }
+// A tile's neighbour indices, [27 taps][rows], tap-major with an odd pitch: the index warps write one map row (27 taps)
+// per instruction and the gather warps read 16 rows of one tap, both without bank conflicts.
+__host__ __device__ constexpr int tab_pitch(int MH) { return MH * TILE_M + 1; }
+__host__ __device__ constexpr int tab_words(int MH) { return 27 * tab_pitch(MH); }
+__host__ __device__ constexpr int aux_bytes(int MH) { return NTAB * tab_words(MH) * 4 + 1024; }
 __host__ __device__ constexpr int num_stages(int BN, int MH, int U = 1) {
   int s = (SMEM_BUDGET - 1024 - aux_bytes(MH)) / (U * stage_bytes(BN, MH));
 #ifdef T2SC_MAX_STAGES
@@ -43,13 +53,32 @@ __host__ __device__ constexpr int num_acc_bufs(int BN, int MH) { return 2 * MH *
 
 struct ConvArgs {
   const void* x; void* y; const uint32_t* nbr; const int* order; const int* src;
-  const PlanTile* tiles; const int* ntiles; int* status;
+  const PlanTile* tiles; const int* tile_lo; const int* tile_hi; int* status;      // this launch covers tiles [*tile_lo, *tile_hi)
   int Ci, Co, n_cot, is_bf16;
-  int npeers, self_rank;    // npeers > 0: map entries are (owner << 29) | row and rows are read from xp[owner]; xp[self_rank] is local
+  int npeers, self_rank;    // npeers > 0: map entries are (owner << PEER_SHIFT) | row and rows are read from xp[owner]; xp[self_rank] is local
   const void* xp[8];
-  int dbg_skip;      // measurement aid (T2SC_DEBUG_SKIP): 1 = no A gather, 2 = no B load, 4 = no MMA (results are then invalid), 8 = CTA 0 prints where each role waited
+  uint32_t n_in;            // rows of x (PEERS: unused, see xp_rows); a map entry at or above it is reported and read as absent
+  uint32_t xp_rows[8];      // PEERS: rows of every peer's array
+  int wait_limit;           // bounded waits give up after this many cycles >> WAIT_LIMIT_SHIFT
+  int dbg_skip;             // diagnostic build only (T2SC_DEBUG_SKIP), always 0 in the shipped library: 1 = no A gather, 2 = no B load,
+                            // 4 = no MMA, 8 = CTA 0 prints where each role waited, 16 = the weight lane never signals its first stage,
+                            // 32 = no neighbour-index loads, 64 = no epilogue
   EpiDev ep;
 };
+
+__device__ __forceinline__ bool diag(const ConvArgs& a, int bits) { return kDiag && (a.dbg_skip & bits) != 0; }
+// Host side: the shipped library always runs with no switch set and the full wait limit; the diagnostic build reads
+// T2SC_DEBUG_SKIP (bit mask above) and T2SC_WAIT_LIMIT_CYCLES from the environment.
+static inline void diag_args(ConvArgs& args) {
+  args.dbg_skip = 0;
+  args.wait_limit = (int)(WAIT_LIMIT_CYCLES >> WAIT_LIMIT_SHIFT);
+#ifdef T2SC_DIAG
+  static const int dbg_skip = [] { const char* e = getenv("T2SC_DEBUG_SKIP"); return e ? atoi(e) : 0; }();
+  static const long long limit = [] { const char* e = getenv("T2SC_WAIT_LIMIT_CYCLES"); return e ? atoll(e) : WAIT_LIMIT_CYCLES; }();
+  args.dbg_skip = dbg_skip;
+  args.wait_limit = (int)((limit >> WAIT_LIMIT_SHIFT) > 0 ? (limit >> WAIT_LIMIT_SHIFT) : 1);
+#endif
+}
 
 // ------------------------------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -82,15 +111,16 @@ __device__ __forceinline__ bool mbar_try_sleep(uint32_t bar, uint32_t parity) {
 // Bounded wait.  After any wait in the CTA has given up, all later waits return at once.
 // Returns false when the wait was given up (now, or earlier by any thread of the CTA): what the barrier guards has then
 // NOT happened, and the caller must not touch memory whose address depends on it.
+// abort_flag[0] is the CTA's "a wait gave up" flag, abort_flag[1] the limit in units of 2^WAIT_LIMIT_SHIFT cycles.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
   if (mbar_try(bar, parity)) return true;
-  long long t0 = clock64();
-  while (!mbar_try_sleep(bar, parity)) {
-    if (*abort_flag || clock64() - t0 > WAIT_LIMIT_CYCLES) { *abort_flag = 1; atomicOr(status, code); return false; }
+  const long long t0 = clock64();
+  for (;;) {
+    if (abort_flag[0] || clock64() - t0 > ((long long)abort_flag[1] << WAIT_LIMIT_SHIFT)) { abort_flag[0] = 1; atomicOr(status, code); return false; }
+    if (mbar_try_sleep(bar, parity)) return true;
   }
-  return true;
 }
-// measurement aid (T2SC_DEBUG_SKIP bit 3): waits that also add their duration to a per-role counter
+// diagnostic build: waits that also add their duration to a per-role counter
 __device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code, bool prof, long long& acc) {
   if (!prof) return mbar_wait(bar, parity, abort_flag, status, code);
   long long t0 = clock64();
@@ -100,6 +130,9 @@ __device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, volat
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
 // arrive on `bar` once all cp.async issued so far by this thread have landed (pending count +1 now, -1 then)
 __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {

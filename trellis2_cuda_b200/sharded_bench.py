@@ -1,29 +1,45 @@
-"""The sharded workload of bench.py (``--workload cfg5``): ONE ~8.6 M-voxel shell in a 2048^3 grid, C = 128, bf16,
-4 stacked submanifold convs, rows cut into equal-count Morton ranges over the ranks, one-voxel halo exchanged
-with one NCCL all-to-all per layer.  Strong scaling: the scene is the same at every N.
+"""The sharded workload of bench.py: ONE ~8.6 M-voxel shell in a 2048^3 grid, C = 128, bf16, 4 stacked submanifold
+convs, rows cut into equal-count Morton ranges over the ranks, one-voxel halo every layer.  Strong scaling: the scene
+is the same at every N.
 
-One step = the 4 layers (halo exchange + conv each).  The neighbour map, halo plan and conv schedule are built
-once before the timed region and reported separately (`setup_ms`), as a decoder level reuses one map for all of
-its blocks.
+One step = the 4 layers (halo exchange + conv each).  Per layer the rank's tiles are run in two parts: the interior
+tiles (no tap reads a halo row) while the halo rows are in flight, the boundary tiles after they have landed.
+
+  * ``--halo nccl``: pack (gather kernel) -> one NCCL all-to-all of feature rows on the communication stream while the
+    interior tiles run -> boundary tiles.
+  * ``--halo p2p``: the feature arrays live in symmetric memory; interior tiles run the ordinary kernel, boundary tiles the
+    peer-memory kernel whose gather reads halo rows straight from the owners' arrays over NVLink.  Per layer the ranks
+    meet at one bounded device-side flag barrier (plain peer stores and loads) so that nobody reads an array its owner is
+    still writing.
+
+The neighbour map, halo plan and conv schedule are built once before the timed region and reported separately
+(`setup_ms`, split into its parts), as a decoder level reuses one map for all of its blocks.
 """
 from __future__ import annotations
 
-import json
 import os
 import time
 
-import numpy as np
 import torch
 import torch.distributed as dist
 
 
-def run(args, rank, world, local_rank, METRIC, peaks, ClockSampler, visible_gpu_index):
+def measure(args, rank, world, local_rank, peaks, ClockSampler, visible_gpu_index, steps=None, warmup=None, halo=None,
+            single_gpu_steps=0, with_e2e=True):
+    """Runs the sharded scene on `world` ranks and returns the result block on rank 0 (None elsewhere).
+    single_gpu_steps > 0: rank 0 afterwards runs the WHOLE scene alone for that many steps, so that the block carries the
+    one-GPU time of the same scene measured in the same run."""
     import trellis2_cuda_b200 as sp
     from trellis2_cuda_b200 import scenes, sharding
 
+    steps = steps or args.steps
+    warmup = warmup if warmup is not None else args.warmup
+    halo = halo or args.halo
     dev = torch.device("cuda", local_rank)
     C, layers, td = 128, args.layers, torch.bfloat16
+    sync = lambda: torch.cuda.synchronize(dev)
     # rank 0 builds the scene, everyone receives the same coordinates
+    t_scene = time.perf_counter()
     if rank == 0:
         coords = torch.from_numpy(scenes.config5_shell(0)).to(dev)
         n_t = torch.tensor([coords.shape[0]], dtype=torch.int64, device=dev)
@@ -35,24 +51,30 @@ def run(args, rank, world, local_rank, METRIC, peaks, ClockSampler, visible_gpu_
     if rank != 0:
         coords = torch.empty((N, 4), dtype=torch.int32, device=dev)
     if world > 1:
-        dist.broadcast(coords, 0)
+        dist.broadcast(coords, 0)          # also the first collective: communicator set-up lands here, not in setup_ms
+    sync()
+    scene_ms = (time.perf_counter() - t_scene) * 1e3
     ctx = sp.context(dev)
     starts = sharding.partition(N, world)
     lo, hi = starts[rank], starts[rank + 1]
+    p2p = halo == "p2p" and world > 1
 
-    p2p = args.halo == "p2p" and world > 1
-    torch.cuda.synchronize()
+    setup = {}
     t0 = time.perf_counter()
     nbr_g, gray = sp.build_neighbors_range(coords, lo, hi)
+    sync(); setup["map_ms"] = (time.perf_counter() - t0) * 1e3
+    t0 = time.perf_counter()
     plan = sharding.build_halo_plan(nbr_g, rank, world, starts)
-    if p2p:      # the conv gathers halo rows from the peers' arrays itself: the map names (owner, row), nothing is copied
-        cache = sp.cache_from_map(coords[lo:hi], sharding.peer_map(nbr_g, starts).contiguous(), gray)
-    else:
-        cache = sp.cache_from_map(coords[lo:hi], plan.nbr_local.contiguous(), gray)
+    sync(); setup["halo_plan_ms"] = (time.perf_counter() - t0) * 1e3
+    t0 = time.perf_counter()
+    nbr_local = plan.nbr_local.contiguous()
+    cache = sp.cache_from_map(coords[lo:hi], nbr_local, gray)
+    split = cache.split_plan_for(C, C, plan.n_own) if world > 1 else None
+    peer_nbr = sharding.peer_map(nbr_g, starts).contiguous() if p2p else None
     del nbr_g
-    st = cache.plan_for(C, C).stats()
-    torch.cuda.synchronize()
-    setup_ms = (time.perf_counter() - t0) * 1e3
+    st = (split or cache.plan_for(C, C)).stats()
+    parts = split.parts() if split is not None else {"interior_tiles": st["tiles"], "boundary_tiles": 0}
+    sync(); setup["schedule_ms"] = (time.perf_counter() - t0) * 1e3
 
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     if p2p:
@@ -61,15 +83,21 @@ def run(args, rank, world, local_rank, METRIC, peaks, ClockSampler, visible_gpu_
         rows_max = max(starts[r + 1] - starts[r] for r in range(world))
         xa = symm.empty((rows_max, C), dtype=td, device=dev)
         xb = symm.empty((rows_max, C), dtype=td, device=dev)
-        ha, hb = symm.rendezvous(xa, dist.group.WORLD), symm.rendezvous(xb, dist.group.WORLD)
+        flags = symm.empty((64,), dtype=torch.int32, device=dev)
+        flags.zero_()
+        ha, hb, hf = symm.rendezvous(xa, dist.group.WORLD), symm.rendezvous(xb, dist.group.WORLD), symm.rendezvous(flags, dist.group.WORLD)
         ptrs = {xa.data_ptr(): [int(p) for p in ha.buffer_ptrs], xb.data_ptr(): [int(p) for p in hb.buffer_ptrs]}
-        hdl = {xa.data_ptr(): ha, xb.data_ptr(): hb}
+        flag_ptrs = [int(p) for p in hf.buffer_ptrs]
+        rows_of = [starts[r + 1] - starts[r] for r in range(world)]
+        dist.barrier()                                  # every rank has zeroed its flags before anyone signals
+        sync()
     else:
         xa = torch.zeros((plan.n_local, C), dtype=td, device=dev)
         xb = torch.zeros((plan.n_local, C), dtype=td, device=dev)
     x0 = torch.randn((plan.n_own, C), generator=g, device=dev).to(td)
     ws = [torch.from_numpy(scenes.kaiming_uniform_weight(C, C, 100 + l)).to(dev).to(td) for l in range(layers)]
-    pack = lambda x_own, idx: sp.gather_rows(x_own, idx, C)
+    send_buf = torch.empty((max(int(plan.send_idx.numel()), 1), C), dtype=td, device=dev)
+    epoch = [0]
 
     def step(timers=None):
         a, b = xa, xb
@@ -77,92 +105,162 @@ def run(args, rank, world, local_rank, METRIC, peaks, ClockSampler, visible_gpu_
         for l in range(layers):
             if timers:
                 timers[0][l].record()
-            if p2p:
-                hdl[a.data_ptr()].barrier(channel=l % 2)       # every rank has written the array this layer reads
-            else:
-                sharding.exchange_halo(plan, a, pack)
-            if timers:
-                timers[1][l].record()
-            if p2p:
-                sp.subm_conv_peers(ptrs[a.data_ptr()], rank, td, C, ws[l], None, cache, out=b[:plan.n_own])
-            else:
+            if world == 1:
                 sp.subm_conv_local(a, ws[l], None, cache, out=b[:plan.n_own])
+            elif p2p:
+                # every rank has written the array this layer reads (and is done reading the one it overwrites)
+                epoch[0] += 1
+                sp.peer_barrier(ctx, flag_ptrs, rank, epoch[0])
+                if timers:
+                    timers[1][l].record()
+                sp.subm_conv_split(a, ws[l], None, cache, split, "interior", out=b[:plan.n_own])
+                sp.subm_conv_peers(ptrs[a.data_ptr()], rows_of, rank, td, C, ws[l], None, cache, out=b[:plan.n_own],
+                                   plan=split, part="boundary", peer_nbr=peer_nbr)
+            else:
+                work = sharding.exchange_halo_async(plan, a, lambda xo, idx: sp.gather_rows(xo, idx, C, out=send_buf))
+                if timers:
+                    timers[1][l].record()
+                sp.subm_conv_split(a, ws[l], None, cache, split, "interior", out=b[:plan.n_own])     # while the halo rows travel
+                if work is not None:
+                    work.wait()
+                sp.subm_conv_split(a, ws[l], None, cache, split, "boundary", out=b[:plan.n_own])
             a, b = b, a
         if p2p:
-            hdl[a.data_ptr()].barrier(channel=0)               # nobody overwrites an array a peer may still be reading
+            epoch[0] += 1
+            sp.peer_barrier(ctx, flag_ptrs, rank, epoch[0])       # nobody overwrites an array a peer may still be reading
         return a
 
-    for _ in range(args.warmup):
+    out = step()
+    ctx.device_status()
+    for _ in range(max(warmup - 1, 0)):
         step()
-    torch.cuda.synchronize()
+    sync()
     sampler = ClockSampler(visible_gpu_index(local_rank))
     if rank == 0:
         sampler.start()
-        time.sleep(0.3)
+        sampler.wait_first_sample()
     if world > 1:
         dist.barrier()
-    torch.cuda.synchronize()
+    sync()
     ev = lambda: torch.cuda.Event(enable_timing=True)
     t_reg0 = time.perf_counter()
     l0 = ctx.launch_count()
     step_ms, exch_ms = [], []
-    for _ in range(args.steps):
+    for _ in range(steps):
         tm = ([ev() for _ in range(layers)], [ev() for _ in range(layers)])
         s, e = ev(), ev()
         s.record()
         step(tm)
         e.record()
-        torch.cuda.synchronize()
+        sync()
         step_ms.append(s.elapsed_time(e))
-        exch_ms.append(sum(tm[0][l].elapsed_time(tm[1][l]) for l in range(layers)))
+        exch_ms.append(sum(tm[0][l].elapsed_time(tm[1][l]) for l in range(layers)) if world > 1 else 0.0)
     launches = ctx.launch_count() - l0
     t_reg1 = time.perf_counter()
     ctx.device_status()
 
-    # end to end: owned features from pinned host memory each step, final features back to the host
-    x_h = x0.cpu().pin_memory()
-    y_h = torch.empty_like(x_h).pin_memory()
     e2e = []
-    for i in range(5):
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        x0.copy_(x_h, non_blocking=True)
-        out = step()
-        y_h.copy_(out[:plan.n_own], non_blocking=True)
-        torch.cuda.synchronize()
-        if i >= 2:
-            e2e.append((time.perf_counter() - t0) * 1e3)
+    if with_e2e:
+        # end to end: owned features from pinned host memory each step, final features back to the host
+        x_h = x0.cpu().pin_memory()
+        y_h = torch.empty_like(x_h).pin_memory()
+        for i in range(5):
+            if world > 1:
+                dist.barrier()
+            sync()
+            t0 = time.perf_counter()
+            x0.copy_(x_h, non_blocking=True)
+            out = step()
+            y_h.copy_(out[:plan.n_own], non_blocking=True)
+            sync()
+            if i >= 2:
+                e2e.append((time.perf_counter() - t0) * 1e3)
     clocks = sampler.stop(t_reg0, t_reg1) if rank == 0 else None
 
     T = st["active_taps"]
-    vals = torch.tensor([sum(step_ms), sum(exch_ms), sum(e2e) / len(e2e), setup_ms], dtype=torch.float64, device=dev)
-    sums = torch.tensor([float(T), float(plan.n_halo), float(st["computed_taps"])], dtype=torch.float64, device=dev)
+    vals = torch.tensor([sum(step_ms), sum(exch_ms), (sum(e2e) / len(e2e)) if e2e else 0.0, setup["map_ms"], setup["halo_plan_ms"],
+                         setup["schedule_ms"], float(parts["boundary_tiles"])], dtype=torch.float64, device=dev)
+    sums = torch.tensor([float(T), float(plan.n_halo), float(st["computed_taps"]), float(parts["interior_tiles"] + parts["boundary_tiles"]),
+                         float(parts["boundary_tiles"])], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
         dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+
+    single = None
+    if single_gpu_steps > 0 and world > 1:
+        # the same scene on ONE GPU, measured on rank 0 in this run (the other ranks wait at the barrier below)
+        del xa, xb
+        if rank == 0:
+            full = sp.build_neighbors(coords, want_sorted=False)
+            xa1 = torch.randn((N, C), generator=g, device=dev).to(td)
+            xb1 = torch.empty_like(xa1)
+            ms1 = []
+            for i in range(single_gpu_steps + 1):
+                s, e = ev(), ev()
+                s.record()
+                a, b = xa1, xb1
+                for l in range(layers):
+                    sp.subm_conv(a, ws[l], None, full, out=b)
+                    a, b = b, a
+                e.record()
+                sync()
+                if i >= 1:
+                    ms1.append(s.elapsed_time(e))
+            single = sum(ms1) / len(ms1)
+            ctx.device_status()
+            del full, xa1, xb1
+        dist.barrier()
     if rank != 0:
-        return
+        return None
     pk, pk_src = peaks()
-    ms = vals[0].item() / args.steps
+    ms = vals[0].item() / steps
     T_all = sums[0].item()
     flops = 2.0 * T_all * C * C * layers
     value = flops / (ms * 1e-3) / 1e12
-    conv_ms = (vals[0].item() - vals[1].item()) / args.steps
     es = 2
-    line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"cfg5: 2048^3 shell of 12 spheres/tori, {layers} stacked 128->128 submanifold convs, equal-count Morton ranges, "
-                                   + ("halo rows read from peer memory by the conv kernel (P2P), one device barrier per layer" if p2p else "one-voxel halo by NCCL all-to-all per layer"), "voxels": N, "Cin": C, "Cout": C, "active_taps": int(T_all),
-                       "computed_taps": int(sums[2].item()), "halo_rows_total": int(sums[1].item()), "step": f"{layers} x (halo exchange + conv)",
+    block = {
+        "workload": f"cfg5: 2048^3 shell of 12 spheres/tori, {layers} stacked 128->128 submanifold convs, equal-count Morton ranges, "
+                    + ("one GPU" if world == 1 else
+                       ("interior tiles by the ordinary kernel, boundary tiles gather their halo rows from peer memory (P2P), one bounded flag barrier per layer"
+                        if p2p else "interior tiles run while one NCCL all-to-all moves the one-voxel halo, boundary tiles after it")),
+        "n_gpus": world, "halo": "none" if world == 1 else halo, "scaling": "strong", "voxels": N, "Cin": C, "Cout": C, "layers": layers,
+        "active_taps": int(T_all), "computed_taps": int(sums[2].item()),
+        "ms_per_step": ms, "tflops": value, "voxels_per_s": N * layers / (ms * 1e-3),
+        "exchange_ms_per_step": vals[1].item() / steps,
+        "exchange_note": "time from a layer's start to the launch of its interior tiles on the slowest rank (pack + enqueue of the all-to-all, or the flag barrier); the transfer itself runs beside the interior tiles",
+        "halo_rows_total": int(sums[1].item()), "halo_bytes_per_layer": int(sums[1].item()) * C * es,
+        "tiles_total": int(sums[3].item()), "boundary_tiles_total": int(sums[4].item()), "boundary_tiles_max_rank": int(vals[6].item()),
+        "setup_ms": {"neighbour_map": vals[3].item(), "halo_plan": vals[4].item(), "schedule": vals[5].item(),
+                     "scene_and_first_collective": scene_ms},
+        "per_gpu_tflops": value / world, "per_gpu_frac_of_sustained_peak": value / world / pk["bf16_tflops_sustained"],
+        "peak_source": f"{pk_src} cuBLAS bf16 sustained",
+        "clocks": clocks, "gpu_launches": launches,
+    }
+    if single is not None:
+        block["single_gpu_ms_per_step"] = single
+        block["speedup_vs_single_gpu"] = single / ms
+    if e2e:
+        block["e2e"] = {"value": flops / (vals[2].item() * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": N * C * es, "d2h_bytes_per_step": N * C * es,
+                        "ms_per_step": vals[2].item(), "path": "owned features from pinned host memory in, 4 layers, final features to pinned host memory"}
+    return block
+
+
+def run(args, rank, world, local_rank, METRIC, peaks, ClockSampler, visible_gpu_index):
+    """`bench.py --workload cfg5`: the sharded scene as the whole JSON line."""
+    import json
+    b = measure(args, rank, world, local_rank, peaks, ClockSampler, visible_gpu_index)
+    if rank != 0:
+        return
+    pk, pk_src = peaks()
+    line = {"metric": METRIC, "value": b["tflops"], "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": b["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": b["workload"], "voxels": b["voxels"], "Cin": 128, "Cout": 128, "active_taps": b["active_taps"],
+                       "computed_taps": b["computed_taps"], "halo_rows_total": b["halo_rows_total"], "step": f"{b['layers']} x (halo exchange + conv)",
                        "l2": "inputs larger than L2 (per-rank features >= 275 MB)"},
-            "voxels_per_s": N * layers / (ms * 1e-3), "exchange_ms_per_step": vals[1].item() / args.steps, "setup_ms": vals[3].item(),
-            "halo_bytes_per_layer": int(sums[1].item()) * C * es,
-            "roofline": {"bound": "tensor", "achieved": flops / world / (conv_ms * 1e-3) / 1e12, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
-                         "frac": flops / world / (conv_ms * 1e-3) / 1e12 / pk["bf16_tflops_sustained"], "traffic": None,
+            "voxels_per_s": b["voxels_per_s"], "exchange_ms_per_step": b["exchange_ms_per_step"], "setup_ms": b["setup_ms"],
+            "halo_bytes_per_layer": b["halo_bytes_per_layer"], "boundary_tiles_total": b["boundary_tiles_total"], "tiles_total": b["tiles_total"],
+            "roofline": {"bound": "tensor", "achieved": b["per_gpu_tflops"], "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                         "frac": b["per_gpu_frac_of_sustained_peak"], "traffic": None,
                          "peak_source": f"{pk_src} cuBLAS bf16 sustained (kernel timed inside a multi-ms step)", "kernel": "k_conv_umma", "per": "GPU"},
-            "clocks": clocks, "gpu_launches": launches,
-            "e2e": {"value": flops / (vals[2].item() * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": N * C * es, "d2h_bytes_per_step": N * C * es,
-                    "ms_per_step": vals[2].item(), "path": "owned features from pinned host memory in, 4 layers, final features to pinned host memory"}}
+            "clocks": b["clocks"], "gpu_launches": b["gpu_launches"], "e2e": b.get("e2e")}
     print(json.dumps(line), flush=True)

@@ -62,22 +62,22 @@ def local_map(nbr_global: torch.Tensor, lo: int, hi: int, starts: List[int]):
     return halo, nbr_local, recv_counts
 
 
-PEER_SHIFT = 29        # map entries of the peer-memory conv: (owner rank << 29) | row inside the owner's array
+PEER_SHIFT = 28        # map entries of the peer-memory conv: (owner rank << 28) | row inside the owner's array (T2SC_PEER_SHIFT)
 
 
 def peer_map(nbr_global: torch.Tensor, starts: List[int]) -> torch.Tensor:
     """No communication and no halo copies: rewrites an owned-rows neighbour map with global indices into the form the
-    peer-memory conv reads, (owner << 29) | (global row - first row of the owner); absent stays -1 (0xffffffff)."""
+    peer-memory conv reads, (owner << 28) | (global row - first row of the owner); absent stays -1 (0xffffffff).  With
+    owners below 8 and rows below 2^28 a present entry never has bit 31 set."""
     world = len(starts) - 1
-    if world > 8 or max(starts[r + 1] - starts[r] for r in range(world)) >= (1 << PEER_SHIFT):
-        raise ValueError("peer maps hold at most 8 ranks and 2^29 rows per rank")
+    if world > 8 or max(starts[r + 1] - starts[r] for r in range(world)) > (1 << PEER_SHIFT):
+        raise ValueError("peer maps hold at most 8 ranks and 2^28 rows per rank")
     g = nbr_global.to(torch.int64)
     present = g >= 0
     bounds = torch.tensor(starts, dtype=torch.int64, device=g.device)
     owner = (torch.searchsorted(bounds, g.clamp(min=0), right=True) - 1).clamp(max=world - 1)
     enc = (owner << PEER_SHIFT) | (g - bounds[owner])
-    enc = torch.where(present, enc, torch.full_like(enc, 0xFFFFFFFF))
-    return (enc & 0xFFFFFFFF).to(torch.int64).where(enc < (1 << 31), enc - (1 << 32)).to(torch.int32)     # same bits in int32 storage
+    return torch.where(present, enc, torch.full_like(enc, -1)).to(torch.int32)     # present entries are below 2^31
 
 
 def build_halo_plan(nbr_global: torch.Tensor, rank: int, world: int, starts: List[int], group=None) -> HaloPlan:
@@ -107,6 +107,69 @@ def exchange_halo(plan: HaloPlan, x_local: torch.Tensor, pack: Callable[[torch.T
         return
     rows = pack(x_local[:plan.n_own], plan.send_idx) if send_buf is None else pack(x_local[:plan.n_own], plan.send_idx, send_buf)
     dist.all_to_all_single(x_local[plan.n_own:], rows, output_split_sizes=plan.recv_counts, input_split_sizes=plan.send_counts, group=group)
+
+
+class PeerLost(RuntimeError):
+    """A peer did not report for a step within the time limit; carries the missing ranks."""
+
+    def __init__(self, step: int, missing: List[int]):
+        super().__init__(f"ranks {missing} did not report for step {step}")
+        self.step, self.missing = step, missing
+
+
+class PeerMonitor:
+    """Host-side liveness check between steps, over a torch.distributed store (no GPU involved): every rank posts
+    `step` before it launches that step's exchange and then waits, with a time limit, until all peers have posted the
+    same step.  A rank that has died, hung or left never posts, so the others raise :class:`PeerLost` on the host
+    BEFORE they enqueue a collective or a kernel that would wait for it on the device; they can then drop the step,
+    re-partition, or shut down with their own GPUs idle and usable."""
+
+    def __init__(self, store, rank: int, world: int, timeout_s: float = 5.0, prefix: str = "t2sc/alive"):
+        self.store, self.rank, self.world, self.timeout_s, self.prefix = store, rank, world, timeout_s, prefix
+
+    def _key(self, step: int, rank: int) -> str:
+        return f"{self.prefix}/{step}/{rank}"
+
+    def post(self, step: int) -> None:
+        self.store.set(self._key(step, self.rank), "1")
+
+    def check(self, step: int) -> None:
+        import datetime
+        import time
+        deadline = time.monotonic() + self.timeout_s
+        missing = [r for r in range(self.world) if r != self.rank]
+        while missing:
+            left = deadline - time.monotonic()
+            if left <= 0:
+                raise PeerLost(step, missing)
+            try:
+                self.store.wait([self._key(step, missing[0])], datetime.timedelta(seconds=max(left, 0.01)))
+                missing.pop(0)
+            except Exception:            # the store's wait timed out (its exception type differs between store kinds)
+                missing = [r for r in missing if not self._posted(step, r)]
+                if missing:
+                    raise PeerLost(step, missing)
+
+    def _posted(self, step: int, rank: int) -> bool:
+        try:
+            return self.store.check([self._key(step, rank)])
+        except Exception:
+            return False
+
+    def step(self, step: int) -> None:
+        self.post(step)
+        self.check(step)
+
+
+def exchange_halo_async(plan: HaloPlan, x_local: torch.Tensor, pack: Callable[[torch.Tensor, torch.Tensor], torch.Tensor], group=None):
+    """Starts the exchange of :func:`exchange_halo` on the process group's communication stream and returns its work
+    handle (None when there is nothing to exchange): the caller runs everything that does not read the halo rows, then
+    ``work.wait()`` (which makes the current stream wait, not the host), then the rest."""
+    if plan.world == 1 or (plan.n_halo == 0 and plan.send_idx.numel() == 0):
+        return None
+    rows = pack(x_local[:plan.n_own], plan.send_idx)
+    return dist.all_to_all_single(x_local[plan.n_own:], rows, output_split_sizes=plan.recv_counts, input_split_sizes=plan.send_counts,
+                                  group=group, async_op=True)
 
 
 def halo_bytes(plan: HaloPlan, channels: int, itemsize: int) -> int:

@@ -11,7 +11,6 @@ from __future__ import annotations
 
 import ctypes
 import dataclasses
-import os
 from typing import Optional
 
 import torch
@@ -95,17 +94,31 @@ def spconv_cfg(N: int, Ci: int, Co: int) -> SpConvCfg:
 
 
 class _Plan:
-    def __init__(self, ctx: Context, nbr, gray, src=None, block_rows: int = 0, tile_rows: int = 0):
+    def __init__(self, ctx: Context, nbr, gray, src=None, block_rows: int = 0, tile_rows: int = 0, n_own: int = 0):
         self.ctx, self.nbr, self.gray, self.src = ctx, nbr, gray, src     # keep the borrowed tensors alive
         m = src.shape[0] if src is not None else nbr.shape[0]
         h = ctypes.c_void_p()
-        ctx.check(ctx.lib.t2sc_plan_create(ctx.h, _ptr(nbr), _ptr(gray), nbr.shape[0], _ptr(src), m, block_rows, tile_rows, ctypes.byref(h)))
+        if n_own:       # one rank of a partitioned scene: interior tiles first, tiles that read halo rows (entries >= n_own) last
+            ctx.check(ctx.lib.t2sc_plan_create_split(ctx.h, _ptr(nbr), _ptr(gray), nbr.shape[0], n_own, block_rows, tile_rows, ctypes.byref(h)))
+        else:
+            ctx.check(ctx.lib.t2sc_plan_create(ctx.h, _ptr(nbr), _ptr(gray), nbr.shape[0], _ptr(src), m, block_rows, tile_rows, ctypes.byref(h)))
         self.h, self.n_out = h, m
+
+    def parts(self):
+        a, b = ctypes.c_int64(), ctypes.c_int64()
+        self.ctx.check(self.ctx.lib.t2sc_plan_parts(self.ctx.h, self.h, ctypes.byref(a), ctypes.byref(b)))
+        return {"interior_tiles": a.value, "boundary_tiles": b.value}
 
     def stats(self):
         t, c, a = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()
         self.ctx.check(self.ctx.lib.t2sc_plan_stats(self.ctx.h, self.h, ctypes.byref(t), ctypes.byref(c), ctypes.byref(a)))
         return {"tiles": t.value, "computed_taps": c.value, "active_taps": a.value}
+
+    def set_input_rows(self, n_in: int) -> None:
+        """The map's entries index a feature array of n_in rows (owned rows + appended halo rows)."""
+        if n_in != getattr(self, "_n_in", self.nbr.shape[0]):
+            self.ctx.check(self.ctx.lib.t2sc_plan_set_input_rows(self.ctx.h, self.h, n_in))
+            self._n_in = n_in
 
     def order(self) -> torch.Tensor:
         o = torch.empty(self.n_out, dtype=torch.int32, device=self.nbr.device)
@@ -154,12 +167,22 @@ class SpConvCache:
         tiles (two accumulators per weight slab) for layers of 128 input channels on maps too large for the L2 (measured:
         8.6 M rows at C = 128 run 3 % faster with them; 218 k rows run 10 % slower; at 64 input channels 128-row tiles
         with two gather groups are the fastest at every size)."""
-        tr = self._tile_rows or int(os.environ.get("T2SC_TILE_ROWS", "0")) or (256 if (self.N > (1 << 18) and Co < 256 and Ci != 64) else 128)
+        tr = self._tile_rows or (256 if (self.N > (1 << 18) and Co < 256 and Ci != 64) else 128)
         if self._plan is None:
             self._plan = {}
         if tr not in self._plan:
             self._plan[tr] = _Plan(self.ctx, self.nbr, self.gray, None, self._block_rows, tr)
         return self._plan[tr]
+
+    def split_plan_for(self, Co: int, Ci: int, n_own: int) -> _Plan:
+        """The schedule of one rank of a partitioned scene whose map indexes owned rows (< n_own) and appended halo rows:
+        same tile height as :meth:`plan_for`, interior tiles first, boundary tiles last (see :func:`subm_conv_split`)."""
+        tr = self._tile_rows or (256 if (self.N > (1 << 18) and Co < 256 and Ci != 64) else 128)
+        if self._plan is None:
+            self._plan = {}
+        if ("split", tr, n_own) not in self._plan:
+            self._plan[("split", tr, n_own)] = _Plan(self.ctx, self.nbr, self.gray, None, self._block_rows, tr, n_own=n_own)
+        return self._plan[("split", tr, n_own)]
 
 
 def build_neighbors(coords: torch.Tensor, W: int = 4096, H: int = 4096, D: int = 4096, want_sorted: bool = True,
@@ -197,22 +220,60 @@ def subm_conv_local(x: torch.Tensor, w: torch.Tensor, b, c: SpConvCache, **kw) -
     """subm_conv whose input has MORE rows than the map (owned rows first, halo rows appended); output [c.N, Co]."""
     if x.shape[0] < c.N:
         raise T2scError(-1, f"spconv shapes: x has {x.shape[0]} rows, cache has {c.N}")
-    return _conv(c.ctx, c.plan_for(w.shape[0], w.shape[2]), x, w, b, w.shape[0], kw.get("ln"), kw.get("act"), kw.get("residual"), kw.get("skip"),
+    plan = c.plan_for(w.shape[0], w.shape[2])
+    plan.set_input_rows(x.shape[0])
+    return _conv(c.ctx, plan, x, w, b, w.shape[0], kw.get("ln"), kw.get("act"), kw.get("residual"), kw.get("skip"),
                  kw.get("variant", "auto"), kw.get("out"))
 
 
-def subm_conv_peers(x_ptrs, rank: int, x_dtype, Ci: int, w: torch.Tensor, b, c: SpConvCache, *, ln=None, act=None, residual=None, out=None):
-    """subm_conv for one rank of a Morton-range partition whose neighbour map holds (owner << 29) | row entries:
+def subm_conv_split(x: torch.Tensor, w: torch.Tensor, b, c: SpConvCache, plan: _Plan, part: str, *, ln=None, act=None,
+                    residual=None, out=None) -> torch.Tensor:
+    """One part ("interior" | "boundary" | "all") of a conv over a split plan (:meth:`SpConvCache.split_plan_for`): x has
+    the owned rows first and the halo rows appended; the interior part reads owned rows only, so it can run while the
+    halo rows are still in flight.  Both parts write into the same `out` [c.N, Co]; the rows of the other part are left
+    untouched."""
+    if x.shape[0] < c.N:
+        raise T2scError(-1, f"spconv shapes: x has {x.shape[0]} rows, cache has {c.N}")
+    _chk(x, "x", None, 2); _chk(w, "w", x.dtype, 3)
+    Ci, Co = x.shape[1], w.shape[0]
+    if w.shape[1] != 27 or w.shape[2] != Ci:
+        raise T2scError(-1, f"spconv shapes: w {tuple(w.shape)} does not match x {tuple(x.shape)}")
+    plan.set_input_rows(x.shape[0])
+    y = out if out is not None else torch.empty((plan.n_out, Co), dtype=x.dtype, device=x.device)
+    e, keep = _epilogue(Co, x.dtype, b, ln, act, residual, None)
+    plan.keep = keep
+    c.ctx.check(c.ctx.lib.t2sc_subm_conv_part(c.ctx.h, plan.h, _ptr(x), _ptr(w), ctypes.byref(e), _ptr(y), _DT[x.dtype], x.shape[0], Ci, Co,
+                                              0, _lib.PART[part]))
+    return y
+
+
+def subm_conv_peers(x_ptrs, x_rows, rank: int, x_dtype, Ci: int, w: torch.Tensor, b, c: SpConvCache, *, ln=None, act=None, residual=None,
+                    out=None, plan: Optional[_Plan] = None, part: str = "all", peer_nbr: Optional[torch.Tensor] = None):
+    """subm_conv for one rank of a Morton-range partition whose neighbour map holds (owner << 28) | row entries:
     the rows are gathered straight from the peers' feature arrays (`x_ptrs[r]` = device address of rank r's array
-    mapped into this process, `x_ptrs[rank]` the local one), so no halo is packed or exchanged.  Returns [c.N, Co]."""
+    mapped into this process, `x_rows[r]` its row count, `x_ptrs[rank]` the local one), so no halo is packed or
+    exchanged.  Returns [c.N, Co].  With `plan` (a split plan over the LOCAL map), `part="boundary"` and `peer_nbr` (the
+    (owner, row) form of the same map) only the boundary tiles take this path; the interior tiles go through
+    :func:`subm_conv_split`."""
     _chk(w, "w", x_dtype, 3)
     Co = w.shape[0]
-    plan = c.plan_for(Co, Ci)
+    plan = plan or c.plan_for(Co, Ci)
     y = out if out is not None else torch.empty((plan.n_out, Co), dtype=x_dtype, device=w.device)
     e, keep = _epilogue(Co, x_dtype, b, ln, act, residual, None)
+    plan.keep = keep + ([peer_nbr] if peer_nbr is not None else [])
     arr = (ctypes.c_void_p * len(x_ptrs))(*[int(p) for p in x_ptrs])
-    c.ctx.check(c.ctx.lib.t2sc_subm_conv_peers(c.ctx.h, plan.h, arr, len(x_ptrs), int(rank), _ptr(w), ctypes.byref(e), _ptr(y), _DT[x_dtype], Ci, Co))
+    rows = (ctypes.c_int64 * len(x_ptrs))(*[int(r) for r in x_rows])
+    c.ctx.check(c.ctx.lib.t2sc_subm_conv_peers_part(c.ctx.h, plan.h, _ptr(peer_nbr), arr, rows, len(x_ptrs), int(rank), _ptr(w), ctypes.byref(e),
+                                                    _ptr(y), _DT[x_dtype], Ci, Co, _lib.PART[part]))
     return y
+
+
+def peer_barrier(ctx: Context, flag_ptrs, rank: int, epoch: int, timeout_ms: int = 2000) -> None:
+    """Enqueues the bounded flag barrier between the ranks of a node (t2sc_peer_barrier): `flag_ptrs[r]` is the device
+    address of rank r's int32 flag array mapped into this process.  A peer that never arrives shows up as
+    T2SC_ERR_DEVICE at the next :meth:`Context.device_status`, not as a hang."""
+    arr = (ctypes.c_void_p * len(flag_ptrs))(*[int(p) for p in flag_ptrs])
+    ctx.check(ctx.lib.t2sc_peer_barrier(ctx.h, arr, len(flag_ptrs), int(rank), int(epoch), int(timeout_ms)))
 
 
 def _epilogue(Co, dtype, bias, ln, act, residual, skip):
@@ -249,6 +310,9 @@ def _conv(ctx, plan, x, w, b, Co, ln, act, residual, skip, variant, out):
         raise T2scError(-1, f"spconv shapes: w {tuple(w.shape)} does not match x {tuple(x.shape)}")
     y = out if out is not None else torch.empty((plan.n_out, Co), dtype=x.dtype, device=x.device)
     e, keep = _epilogue(Co, x.dtype, b, ln, act, residual, skip)
+    # The kernel runs on the context's stream (the torch stream that was current when the cache was built), which need
+    # not be the stream torch's allocator associates with these temporaries: the plan holds them until its next conv.
+    plan.keep = keep
     ctx.check(ctx.lib.t2sc_subm_conv(ctx.h, plan.h, _ptr(x), _ptr(w), ctypes.byref(e), _ptr(y), _DT[x.dtype],
                                      x.shape[0], Ci, Co, _VARIANT[variant]))
     return y
@@ -313,11 +377,11 @@ def subdiv_conv(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], lev
     return _conv(level.parent.ctx, level.up_plan, x, w, b, w.shape[0] // 8, ln, act, None, None, variant, out)
 
 
-def gather_rows(x: torch.Tensor, src: torch.Tensor, C: int) -> torch.Tensor:
+def gather_rows(x: torch.Tensor, src: torch.Tensor, C: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y[r] = x.view(-1, C)[src[r]] (src/sdec.cu:34-37)."""
     _chk(x, "x"); _chk(src, "src", torch.int32, 1)
     ctx = context(x.device)
-    y = torch.empty((src.shape[0], C), dtype=x.dtype, device=x.device)
+    y = out[:src.shape[0]] if out is not None else torch.empty((src.shape[0], C), dtype=x.dtype, device=x.device)
     ctx.check(ctx.lib.t2sc_gather_rows(ctx.h, _ptr(x), _ptr(src), src.shape[0], C, _DT[x.dtype], _ptr(y)))
     return y
 
