@@ -425,7 +425,7 @@ def run_cfg3(args, rank, world, local_rank, dev):
         mark(1)
         lv = sp.subdivide(parent, flags)
         mark(2)
-        _ = lv.up_plan, lv.nb.plan_for(Cc, Cc)
+        _ = lv.up_plan_for(Cc), lv.nb.plan_for(Cc, Cc)
         mark(3)
         up = sp.subdiv_conv(x, w1, None, lv)
         mark(4)
@@ -435,7 +435,7 @@ def run_cfg3(args, rank, world, local_rank, dev):
 
     lv, y = step()
     m = lv.coords.shape[0]
-    st1, st2 = lv.up_plan.stats(), lv.nb.plan_for(Cc, Cc).stats()
+    st1, st2 = lv.up_plan_for(Cc).stats(), lv.nb.plan_for(Cc, Cc).stats()
     flops = [0, 0, 0, 2.0 * st1["active_taps"] * Ci * Cc, 2.0 * st2["active_taps"] * Cc * Cc]
     byts = [n * 16 + n * 27 * 4 + n * 4, n * 8 + m * 16 + m * 4 + m * 16 + m * 27 * 4 + m * 4, 0,
             alg_bytes(n, m, Ci, Cc, 8 * Cc, es), alg_bytes(m, m, Cc, Cc, Cc, es)]
@@ -539,7 +539,7 @@ def run_cfg4(args, rank, world, local_rank, dev):
             if evs:
                 evs[l][3].record()
             if info is not None:
-                st = lv.up_plan.stats()
+                st = lv.up_plan_for(C // 2).stats()
                 info[-1].update(up_tiles=st["tiles"], up_active_taps=st["active_taps"], up_computed_taps=st["computed_taps"])
             cache = lv.nb
         return x

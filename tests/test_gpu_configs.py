@@ -162,7 +162,7 @@ def test_config4_stack_at_its_stated_widths(sp):
 # ------------------------------------------------------------------------------------------ configuration 5
 def test_config5_scene_on_one_gpu(sp):
     """The 8,597,581-voxel shell of the sharded configuration (2048^3, C = 128, bf16) on one GPU with the default plan
-    for that size (256-row tiles, mask sort inside runs of 65,536 rows): the whole map bit for bit, the conv on sampled
+    for that size (128-row tiles, mask sort inside runs of 65,536 rows): the whole map bit for bit, the conv on sampled
     rows, two stacked layers, and the agreement of the 128-row and 256-row schedules."""
     dt, td = "bf16", torch.bfloat16
     c = scenes.config5_shell()
@@ -192,5 +192,5 @@ def test_config5_scene_on_one_gpu(sp):
         check_feats(host(y[rows_t]), oracle_rows(x, w), f"config 5 layer {layer}")
         x = y
     cache.ctx.device_status()
-    other = sp.cache_from_map(cache.coords, cache.nbr, cache.gray, tile_rows=128)
+    other = sp.cache_from_map(cache.coords, cache.nbr, cache.gray, tile_rows=256)
     assert torch.equal(sp.subm_conv(x, w, None, other), sp.subm_conv(x, w, None, cache))     # same accumulation order per row

@@ -34,6 +34,9 @@ struct t2sc_plan {
   const uint32_t* nbr = nullptr;  // borrowed
   const int32_t* src = nullptr;   // borrowed (NULL for a submanifold plan)
   int32_t* order = nullptr;     // [n_out] output row handled at each plan position
+  uint32_t* tnbr = nullptr;     // [max_tiles][27][tile_rows]: the map in tile order, tap-major, absent = 0x80000000 (what a tile's
+                                // CTA copies into shared memory with one bulk copy)
+  i64 table_n_in = -1;          // n_in the table was last checked against (-1: not yet)
   PlanTile* tiles = nullptr;    // [max_tiles]
   int* bounds = nullptr;        // device [3]: {0, first boundary tile, realised tile count}; parts are [b0,b1) and [b1,b2)
   int* ntiles = nullptr;        // = bounds + 2: realised tile count (<= max_tiles)
@@ -118,6 +121,7 @@ static inline EpiDev epi_dev(const t2sc_epilogue* e) {
   return d;
 }
 
+int plan_table_prepare(t2sc_ctx* ctx, t2sc_plan* plan, i64 n_in);      // plan.cu: table bounds-checked against n_in (once per n_in)
 // implemented in the kernel files
 // which tiles of a plan a launch covers: pointers to the first tile index and to the index one past the last
 struct TilePart { const int* lo; const int* hi; };

@@ -37,26 +37,34 @@ using namespace umma;
 // ------------------------------------------------------------------------------------------ kernel
 // Warp roles: 0-3 gather A (cp.async), 4 weights (TMA), 5 and the last warp of the base set fill the neighbour-index table,
 // 6 MMA issue + TMEM owner, 7.. epilogue (4 warps per 128-row half).
-// One pipeline stage holds one unit = one (tap, 64-channel chunk).
-// G = gather groups of four warps.  G = 1: the four gather warps fill every unit together.  G = 2 (128-row tiles):
-// a second group of four warps sits behind the epilogue warps and the groups fill alternate units, so one group's
+// A unit is one (tap, 64-channel chunk): 16 KB of gathered rows per 128-row half, one weight slab, four MMAs per half.
+// One pipeline stage holds U consecutive units of a tile.  Every role pays one barrier round trip per STAGE (a wait
+// that answers after ~100 clocks, an arrival or commit), in order, whatever the stage holds; with one unit per stage
+// that is ~400 clocks per unit against 64 to 256 clocks of tensor time at Co <= 128, so narrow layers take U = 2 or 4.
+// G = gather groups of four warps.  G = 1: the four gather warps fill every stage together.  G = 2 (128-row tiles):
+// a second group of four warps sits behind the epilogue warps and the groups fill alternate stages, so one group's
 // barrier round trips and index reads overlap the other group's copies.
 //
-// Neighbour indices reach the gather warps through a per-TILE table in shared memory ([27 taps][rows], two buffers): the
-// two index warps copy the tile's map rows into it with 4-byte cp.async (one 108-byte map row per warp instruction, all
-// rows of the tile in flight at once), mark absent / out-of-range entries, and hand the whole tile over with ONE barrier.
-// (Delivering one tap at a time through a ring made every tap wait for a dependent load of the index warp: with one or
-// two units per tap, at 64 and 128 input channels, that latency was the kernel's time.)
-template <int BN, int MH, int G, bool PEERS, class T>
+// Neighbour indices reach the gather warps through a per-TILE table in shared memory ([27 taps][rows], two buffers).  The
+// plan keeps the map in exactly that form, tile by tile, so one lane fetches a tile's table with ONE bulk copy (13.8 KB
+// per 128 rows) a tile ahead and the gather warps meet one barrier per tile.  A warp issues roughly one instruction per ten
+// clocks here, so anything that costs instructions per (row, tap) in the kernel - a ring slot per tap, or warps that
+// transpose map rows into the table - took longer than the tile's MMAs at 64 and 128 channels.
+// Only the peer-memory form, whose map arrives with the call, still has two index warps that build the table from map
+// rows (4-byte cp.async, one 108-byte row per warp instruction), mark absent / out-of-range entries and flag the taps
+// that read a peer.
+template <int BN, int MH, int G, int U, bool PEERS, class T>
 __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __grid_constant__ CUtensorMap tmw, const ConvArgs a) {
   static_assert(G == 1 || (G == 2 && MH == 1), "a second gather group only fits beside 128-row tiles");
-  constexpr int STAGE = stage_bytes(BN, MH);         // MH gathered A halves + one weight slab
-  constexpr int S = num_stages(BN, MH);
+  constexpr int UNIT = stage_bytes(BN, MH);          // MH gathered A halves + one weight slab
+  constexpr int STAGE = U * UNIT;
+  constexpr int S = num_stages(BN, MH, U);
   constexpr int B_BYTES = BN * 128;
   constexpr int NB = num_acc_bufs(BN, MH);            // accumulator buffers, each MH halves of BN columns
   constexpr int TMEM_COLS = NB * MH * BN < 32 ? 32 : NB * MH * BN;
   constexpr int ROWS = MH * TILE_M;
-  constexpr int PITCH = tab_pitch(MH), TABW = tab_words(MH);
+  constexpr int PITCH = PEERS ? tab_pitch(MH) : ROWS;  // the index warps write a map row per instruction: an odd pitch keeps that conflict-free
+  constexpr int TABW = 27 * PITCH;
   constexpr int NGW = 4 * G;                          // gather warps
 
   extern __shared__ uint8_t smem_raw[];
@@ -78,7 +86,7 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, NUM_PROD_THREADS + 1); mbar_init(bar_empty + 8 * s, 1); }
     for (int b = 0; b < 2; b++) { mbar_init(bar_accf + 8 * b, 1); mbar_init(bar_acce + 8 * b, 128 * MH); }
-    for (int r = 0; r < NTAB; r++) { mbar_init(bar_tready + 8 * r, 2); mbar_init(bar_tfree + 8 * r, NGW); }   // two index warps fill, every gather warp releases
+    for (int r = 0; r < NTAB; r++) { mbar_init(bar_tready + 8 * r, PEERS ? 2 : 1); mbar_init(bar_tfree + 8 * r, NGW); }   // two index warps (or the one loader lane) fill, every gather warp releases
     for (int r = 0; r < NTAB * 64; r++) tab_remote[r] = 0;
     abort_flag[0] = 0; abort_flag[1] = a.wait_limit;
     if (PEERS) for (int r = 0; r < 8; r++) { peer_base[r] = a.xp[r]; peer_rows[r] = a.xp_rows[r]; }
@@ -114,56 +122,60 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
       const uint32_t buf = tt % NTAB;
       // Every gather warp waits for every tile's table, also one that has none of the tile's units (G == 2): a warp can
       // then never release a buffer twice within one phase of its barrier.
+      if (threadIdx.x == 0) trace(a, 0, 0, tt);
       alive &= mbar_wait_t(bar_tready + 8 * buf, (tt / NTAB) & 1, abort_flag, a.status, 32, prof, w_idx);
+      if (threadIdx.x == 0) trace(a, 0, 1, tt);
       const uint32_t* tab = itab + buf * TABW + jbase;
-      for (uint32_t mk = tile.mask; mk;) {
-        const int v = __ffs(mk) - 1;
-        mk &= mk - 1;
-        if (G == 2 && nchunk == 1 && (int)(it & 1) != g) {     // one unit per tap: the other group's tap
-          it++;
-          if (!mk) { __syncwarp(); if (lane == 0 && alive) mbar_arrive(bar_tfree + 8 * buf); }
+      const int nunits = __popc(tile.mask) * nchunk;
+      uint32_t mk = tile.mask;        // taps still to come; the current tap is its lowest set bit, c the current chunk
+      int c = 0, held_tap = -1;       // held_tap: the tap whose indices are in idx[] / sz[] / rp[]
+      uint32_t idx[8 * MH], sz[8 * MH];       // rows jbase + 16 i; rows 128.. are the second half, stored right behind the first
+      const T* rp[PEERS ? 8 * MH : 1];
+      bool remote = false;
+      for (int u0 = 0; u0 < nunits; u0 += U, it++) {
+        const int nu = nunits - u0 < U ? nunits - u0 : U;      // a tile's last stage may be short
+        // G == 2: the groups alternate stages.  A group waits on stages two apart, never more than the stage count apart,
+        // so it cannot run two phases ahead of a stage, where a parity wait would pass by mistake.
+        if (G == 2 && (int)(it & 1) != g) {
+          for (int k = 0; k < nu; k++) if (++c == nchunk) { c = 0; mk &= mk - 1; }
           continue;
         }
-        // Table entries: row number (PEERS: (owner << PEER_SHIFT) | row), or RING_ABSENT.  Everything that does not depend on
-        // the channel chunk is done here, once per tap, so that a copy costs two instructions (address, cp.async): the gather
-        // warps run these in order and their instruction count per unit is what bounds narrow layers.
-        uint32_t idx[8 * MH], sz[8 * MH];       // rows jbase + 16 i; rows 128.. are the second half, stored right behind the first
+        const uint32_t st = it % S;
+        alive &= mbar_wait_t(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 1, prof, w_empty);
+        if ((threadIdx.x & 127) == 0) trace(a, 4, 3, it);          // stage-level events (first 64 stages): the gather group holds a free stage
 #pragma unroll
-        for (int i = 0; i < 8 * MH; i++) idx[i] = tab[v * PITCH + 16 * i];
-        // PEERS: almost every tap reads local rows only (the index warps say so per tap) and takes the plain path with the
-        // owner bits masked off.  For a tap with rows of a peer the addresses are formed here: a table load between the
-        // copies below would be ordered after each of them and serialise the loop.
-        const T* rp[PEERS ? 8 * MH : 1];
-        bool remote = false;
-        if constexpr (PEERS) {
-          remote = (tab_remote[buf * 64 + v] | tab_remote[buf * 64 + 32 + v]) != 0;
-          if (__builtin_expect(remote, 0)) {
+        for (int k = 0; k < U; k++) {
+          if (k >= nu) break;
+          const int v = __ffs(mk) - 1;
+          if (v != held_tap) {
+            held_tap = v;
+            // Table entries: row number (PEERS: (owner << PEER_SHIFT) | row), or RING_ABSENT.  Everything that does not
+            // depend on the channel chunk is done here, once per tap, so that a copy costs two instructions (address,
+            // cp.async): the gather warps run these in order.
 #pragma unroll
-            for (int i = 0; i < 8 * MH; i++)
-              rp[i] = idx[i] != RING_ABSENT ? (const T*)peer_base[idx[i] >> PEER_SHIFT] + (i64)(idx[i] & PEER_ROW_MASK) * a.Ci + c16 * 8 : x;
+            for (int i = 0; i < 8 * MH; i++) idx[i] = tab[v * PITCH + 16 * i];
+            // PEERS: almost every tap reads local rows only (the index warps say so per tap) and takes the plain path with
+            // the owner bits masked off.  For a tap with rows of a peer the addresses are formed here: a table load between
+            // the copies below would be ordered after each of them and serialise the loop.
+            if constexpr (PEERS) {
+              remote = (tab_remote[buf * 64 + v] | tab_remote[buf * 64 + 32 + v]) != 0;
+              if (__builtin_expect(remote, 0)) {
+#pragma unroll
+                for (int i = 0; i < 8 * MH; i++)
+                  rp[i] = idx[i] != RING_ABSENT ? (const T*)peer_base[idx[i] >> PEER_SHIFT] + (i64)(idx[i] & PEER_ROW_MASK) * a.Ci + c16 * 8 : x;
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 8 * MH; i++) {
+              sz[i] = (~idx[i] >> 27) & 16u;                                 // 16 bytes, or 0 = zero-fill for an absent neighbour
+              idx[i] &= PEERS ? PEER_ROW_MASK : 0x7FFFFFFFu;                 // absent -> row 0, a valid address that is not read
+            }
           }
-        }
-#pragma unroll
-        for (int i = 0; i < 8 * MH; i++) {
-          sz[i] = (~idx[i] >> 27) & 16u;                                 // 16 bytes, or 0 = zero-fill for an absent neighbour
-          idx[i] &= PEERS ? PEER_ROW_MASK : 0x7FFFFFFFu;                 // absent -> row 0, a valid address that is not read
-        }
-        if (!mk) {        // the tile's last tap is in registers: the index warps may refill this table
-          __syncwarp();
-          if (lane == 0 && alive) mbar_arrive(bar_tfree + 8 * buf);
-        }
-        for (int c = 0; c < nchunk; c++, it++) {
-          // G == 2, several units per tap: the groups alternate units.  A group waits on units two apart, never more than the
-          // stage count apart, so it cannot run two phases ahead of a stage, where a parity wait would pass by mistake.
-          if (G == 2 && nchunk > 1 && (int)(it & 1) != g) continue;
-          const uint32_t st = it % S;
-          alive &= mbar_wait_t(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 1, prof, w_empty);
-          const uint32_t dst = smem_base + st * STAGE + dst_thread;
-          const T* xs = x + c * KCH + c16 * 8;
           // After a wait was given up this thread loads and signals nothing more: the table may hold anything, and an
           // arrival on a barrier whose phase is still waiting for bytes in flight would overrun its count.
-          if (!alive) continue;
-          if (!diag(a, 1)) {
+          if (alive && !diag(a, 1)) {
+            const uint32_t dst = smem_base + st * STAGE + k * UNIT + dst_thread;
+            const T* xs = x + c * KCH + c16 * 8;
             if (PEERS && __builtin_expect(remote, 0)) {          // one branch per unit, not per copy: a P2P load when the owner is a peer
 #pragma unroll
               for (int i = 0; i < 8 * MH; i++) cp_async16(dst + i * (16 * 128), rp[i] + c * KCH, sz[i]);
@@ -172,9 +184,15 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
               for (int i = 0; i < 8 * MH; i++) cp_async16(dst + i * (16 * 128), xs + (i64)idx[i] * a.Ci, sz[i]);
             }
           }
-          cp_async_arrive_noinc(bar_full + 8 * st);     // this thread's arrival, delivered when its copies have landed
+          if (++c == nchunk) { c = 0; mk &= mk - 1; }
         }
+        if (alive) cp_async_arrive_noinc(bar_full + 8 * st);     // this thread's arrival, delivered when its copies have landed
+        if ((threadIdx.x & 127) == 0) trace(a, 0, 3, it);          // ... has issued its copies
       }
+      // the tile's last indices are in registers: the index warps may refill this table
+      __syncwarp();
+      if (lane == 0 && alive) mbar_arrive(bar_tfree + 8 * buf);
+      if (threadIdx.x == 0) trace(a, 0, 2, tt);
     }
     cp_async_wait_all();
     if (prof && blockIdx.x == 0 && threadIdx.x == 0)
@@ -190,25 +208,50 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
         const PlanTile tile = tile_next;
         if (item + (int)gridDim.x < nitems) tile_next = tiles[(item + gridDim.x) / a.n_cot];
         const int wrow = tile.wbase * a.Co + cot * BN;
-        for (uint32_t mk = tile.mask; mk && alive; mk &= mk - 1) {
-          const int v = __ffs(mk) - 1;
-          for (int c = 0; c < nchunk; c++, it++) {
-            const uint32_t st = it % S;
-            alive &= mbar_wait(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 2);
-            if (!alive) break;
-            if (diag(a, 16) && it == 0) continue;        // bounded-wait test: this stage never fills, the MMA lane's wait runs out
+        const int nunits = __popc(tile.mask) * nchunk;
+        uint32_t mk = tile.mask;
+        int c = 0;
+        for (int u0 = 0; u0 < nunits; u0 += U, it++) {
+          const int nu = nunits - u0 < U ? nunits - u0 : U;
+          const uint32_t st = it % S;
+          alive &= mbar_wait(bar_empty + 8 * st, ((it / S) & 1) ^ 1, abort_flag, a.status, 2);
+          if (!alive) break;
+          trace(a, 1, 1, it);                                      // ... the weight lane holds the stage
+          const bool mute = diag(a, 16) && it == 0;      // bounded-wait test: this stage never fills, the MMA lane's wait runs out
+          if (!mute) {
             if (diag(a, 2)) mbar_arrive(bar_full + 8 * st);
-            else {
-              mbar_arrive_expect_tx(bar_full + 8 * st, B_BYTES);
-              tma_load_3d(smem_base + st * STAGE + MH * A_BYTES, &tmw, c * KCH, v, wrow, bar_full + 8 * st);
-            }
+            else mbar_arrive_expect_tx(bar_full + 8 * st, nu * B_BYTES);
+          }
+#pragma unroll
+          for (int k = 0; k < U; k++) {
+            if (k >= nu) break;
+            if (!mute && !diag(a, 2))
+              tma_load_3d(smem_base + st * STAGE + k * UNIT + MH * A_BYTES, &tmw, c * KCH, __ffs(mk) - 1, wrow, bar_full + 8 * st);
+            if (++c == nchunk) { c = 0; mk &= mk - 1; }
           }
         }
+        trace(a, 1, 0, (uint32_t)((item - blockIdx.x) / gridDim.x));
+      }
+    }
+    __syncwarp();
+  } else if (!PEERS && (warp == WARP_IDX || warp == warp_idx2(MH))) {
+    // ===================================================================== neighbour-index table: one bulk copy per tile
+    if (warp == WARP_IDX && lane == 0) {
+      uint32_t tt = 0;
+      for (int item = blockIdx.x; item < nitems; item += gridDim.x, tt++) {
+        const uint32_t buf = tt % NTAB;
+        trace(a, 2, 0, tt);
+        if (!mbar_wait(bar_tfree + 8 * buf, ((tt / NTAB) & 1) ^ 1, abort_flag, a.status, 64)) break;
+        trace(a, 2, 1, tt);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the gather warps' reads of this buffer come before the copy's writes
+        mbar_arrive_expect_tx(bar_tready + 8 * buf, TABW * 4);
+        bulk_load(smem_u32(itab + buf * TABW), a.tnbr + (i64)(tile0 + item / a.n_cot) * TABW, TABW * 4, bar_tready + 8 * buf);
+        trace(a, 2, 3, tt);
       }
     }
     __syncwarp();
   } else if (warp == WARP_IDX || warp == warp_idx2(MH)) {
-    // ===================================================================== neighbour-index table, one per tile
+    // ===================================================================== peer-memory form: neighbour-index table built from map rows
     // Two index warps, each serving half of the tile's rows, one tile ahead of the gather warps.  Tile descriptors are
     // fetched two tiles ahead and row numbers one tile ahead, so no dependent load sits on a tile boundary; the map rows
     // themselves go from global to shared memory by cp.async, a whole half tile in flight at once and no register per entry.
@@ -235,7 +278,9 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
       const uint32_t buf = tt % NTAB;
       // warp-uniform: the fill below is a warp-wide exchange of row numbers, and after a wait was given up nothing more
       // is written or signalled
+      if (ih == 0 && lane == 0) trace(a, 2, 0, tt);
       if (!__all_sync(0xffffffffu, mbar_wait_t(bar_tfree + 8 * buf, ((tt / NTAB) & 1) ^ 1, abort_flag, a.status, 64, prof, w_free))) break;
+      if (ih == 0 && lane == 0) trace(a, 2, 1, tt);
       uint32_t* tab = itab + buf * TABW + ih * HROWS;
       long long t_l0 = prof ? clock64() : 0;
 #pragma unroll
@@ -252,6 +297,7 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
       }
       cp_async_wait_all();
       __syncwarp();
+      if (ih == 0 && lane == 0) trace(a, 2, 2, tt);
       if (prof) w_load += clock64() - t_l0;
       // Second pass over the landed entries, lane = tap: absent and out-of-range entries become RING_ABSENT (bit 31), and
       // in the peer-memory form each tap learns whether any of its rows lives on another rank.
@@ -274,6 +320,7 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tready + 8 * buf);
+      if (ih == 0 && lane == 0) trace(a, 2, 3, tt);
 #pragma unroll
       for (int i = 0; i < NR; i++) nr[i] = nr_next[i];
       tile_n0 = tile_n1; tile_n1 = tile_n2;
@@ -285,6 +332,7 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
     // ===================================================================== MMA issuer: one lane waits, issues and commits
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(BN, a.is_bf16);
+      const uint64_t desc0 = umma_desc(smem_base);      // every operand's descriptor is this + (its byte offset >> 4): the start-address field cannot overflow within 227 KB
       uint32_t it = 0, acc_it = 0;
       bool alive = true;        // false once a wait was given up: no more MMAs or commits
       const bool prof = diag(a, 8); long long w_full = 0, w_acc = 0, w_issue = 0, w_commit = 0, t_role = clock64();
@@ -293,34 +341,44 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
         const PlanTile tile = tile_next;
         if (item + (int)gridDim.x < nitems) tile_next = tiles[(item + gridDim.x) / a.n_cot];
         const uint32_t buf = acc_it % NB, aph = (acc_it / NB) & 1;
+        trace(a, 3, 0, acc_it);
         alive &= mbar_wait_t(bar_acce + 8 * buf, aph ^ 1, abort_flag, a.status, 4, prof, w_acc);
         if (!alive) break;
+        trace(a, 3, 1, acc_it);
         tc_fence_after();                       // the epilogue's tcgen05.ld of this buffer come before the MMAs that overwrite it
         const uint32_t d_tmem = tmem_base + buf * (MH * BN);
         const int halves = tile.rows > TILE_M ? MH : 1;
         const int nunits = __popc(tile.mask) * nchunk;
-        for (int u = 0; u < nunits; u++, it++) {
+        for (int u0 = 0; u0 < nunits; u0 += U, it++) {
+          const int nu = nunits - u0 < U ? nunits - u0 : U;
           const uint32_t s = it % S, ph = (it / S) & 1;
           // No tcgen05 fence after this wait (the operands are shared-memory data published by the barrier, not tcgen05
           // results) and no proxy fence either: the copies' completion is delivered through the barrier itself
           // (cp.async.mbarrier.arrive.noinc); a fence.proxy.async here was measured at 3-12 % of the kernel time.
+          trace(a, 3, 3, it);                                      // ... the MMA lane starts waiting for it
           alive &= mbar_wait_t(bar_full + 8 * s, ph, abort_flag, a.status, 8, prof, w_full);
           if (!alive) break;
+          trace(a, 1, 2, it);                                      // ... the stage is full
           long long ti0 = prof ? clock64() : 0;
           if (!diag(a, 4)) {
-            const uint64_t bd = umma_desc(smem_base + s * STAGE + MH * A_BYTES);
-            for (int h = 0; h < halves; h++) {
-              const uint64_t ad = umma_desc(smem_base + s * STAGE + h * A_BYTES);
+            const uint64_t ds = desc0 + (uint64_t)(s * (STAGE >> 4));          // descriptor of the stage's first byte
 #pragma unroll
-              for (int kk = 0; kk < KCH / 16; kk++)    // +32 bytes along K inside the swizzle row = +2 in the address field
-                tc_mma(d_tmem + h * BN, ad + 2 * kk, bd + 2 * kk, idesc, (u > 0 || kk > 0) ? 1u : 0u);
+            for (int k = 0; k < U; k++) {
+              if (k >= nu) break;
+#pragma unroll
+              for (int h = 0; h < MH; h++) {
+                if (h < halves)
+                  tc_mma_k64(d_tmem + h * BN, ds + ((k * UNIT + h * A_BYTES) >> 4), ds + ((k * UNIT + MH * A_BYTES) >> 4), idesc, u0 + k > 0 ? 1u : 0u);
+              }
             }
           }
           long long ti1 = prof ? clock64() : 0;
           tc_commit(bar_empty + 8 * s);
+          trace(a, 1, 3, it);                                      // ... its MMAs are issued and the commit is behind them
           if (prof) { w_issue += ti1 - ti0; w_commit += clock64() - ti1; }
         }
         if (alive) tc_commit(bar_accf + 8 * buf);
+        trace(a, 3, 2, acc_it);
       }
       if (prof && blockIdx.x == 0)
         printf("[t2sc prof] mma: total %lld clk, wait stage full %lld, wait accumulator free %lld, mma issue %lld, commit %lld, steps %u, tiles %u\n",
@@ -344,12 +402,15 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
       int sp = 0, ss = 0;
       if (has_skip && orow >= 0) { int sv = a.ep.skip_src[orow]; sp = sv >> 3; ss = sv & 7; }
       // warp-uniform (tcgen05.ld is warp-collective); after a wait was given up nothing more is read or signalled
+      if (warp == WARP_EPI0 && lane == 0) trace(a, 4, 0, acc_it);
       if (!__all_sync(0xffffffffu, mbar_wait_t(bar_accf + 8 * buf, aph, abort_flag, a.status, 16, prof, w_accf))) break;
+      if (warp == WARP_EPI0 && lane == 0) trace(a, 4, 1, acc_it);
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (MH * BN) + half * BN;
       if (!diag(a, 64)) epilogue_row<BN, T>(a, taddr, orow, cot, wcol0, sp, ss);
       tc_fence_before();
       mbar_arrive(bar_acce + 8 * buf);
+      if (warp == WARP_EPI0 && lane == 0) trace(a, 4, 2, acc_it);
     }
     if (prof && blockIdx.x == 0 && warp == WARP_EPI0 && lane == 0)
       printf("[t2sc prof] epilogue: total %lld clk, wait accumulator full %lld (busy %lld), tiles %u\n", clock64() - t_role, w_accf, clock64() - t_role - w_accf, acc_it);
@@ -381,30 +442,41 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-template <int BN, int MH, int G, bool PEERS, class T>
+template <int BN, int MH, int G, int U, bool PEERS, class T>
 int launch_p(t2sc_ctx* ctx, const CUtensorMap& tm, const ConvArgs& args, i64 max_items) {
-  constexpr int smem = num_stages(BN, MH) * stage_bytes(BN, MH) + aux_bytes(MH) + 1024;
-  static_assert(smem <= SMEM_BUDGET && num_stages(BN, MH) >= 2, "shared memory budget");
+  constexpr int smem = num_stages(BN, MH, U) * U * stage_bytes(BN, MH) + aux_bytes(MH) + 1024;
+  static_assert(smem <= SMEM_BUDGET && num_stages(BN, MH, U) >= 2, "shared memory budget");
   static bool attr_set[16] = {};
   if (!attr_set[ctx->device & 15]) {
-    T2_CUDA(ctx, cudaFuncSetAttribute(k_conv_umma<BN, MH, G, PEERS, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    T2_CUDA(ctx, cudaFuncSetAttribute(k_conv_umma<BN, MH, G, U, PEERS, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set[ctx->device & 15] = true;
   }
   int grid = (int)(max_items < ctx->num_sms ? max_items : ctx->num_sms);
-  k_conv_umma<BN, MH, G, PEERS, T><<<grid, num_threads(MH, G), smem, ctx->stream>>>(tm, args);
+  k_conv_umma<BN, MH, G, U, PEERS, T><<<grid, num_threads(MH, G), smem, ctx->stream>>>(tm, args);
   T2_LAUNCHED(ctx);
   return T2SC_OK;
 }
 
-// Gather groups: two for 64 input channels on 128-row tiles (one unit per tap: measured 16-19 % faster; equal at 128
-// channels, 3 % slower at 256), else one.  The peer-memory form has one group.
+// Which form runs.  128-row tiles with Co <= 128 (accumulator tiles of 32..128 columns): two gather groups and two units
+// per stage (measured 5-12 % faster than one unit per stage at 64 and 128 channels; four units per stage are no better
+// than two).  Co % 256 == 0: one unit per stage (a stage is 48 KB there), the second gather group only for Ci = 64.
+// 256-row tiles and the peer-memory form: one group, one unit per stage.  The diagnostic build can force one unit per
+// stage (T2SC_UNITS=1) to compare the forms.
 template <int BN, int MH, class T>
 int launch_bn(t2sc_ctx* ctx, const CUtensorMap& tm, const ConvArgs& args, i64 max_items) {
-  if (args.npeers > 0) return launch_p<BN, MH, 1, true, T>(ctx, tm, args, max_items);
-  if constexpr (MH == 1) {
-    if (args.Ci == KCH) return launch_p<BN, MH, 2, false, T>(ctx, tm, args, max_items);
+  if (args.npeers > 0) return launch_p<BN, MH, 1, 1, true, T>(ctx, tm, args, max_items);
+  if constexpr (MH == 1 && BN <= 128) {
+#ifdef T2SC_DIAG
+    static const int force_u = [] { const char* e = getenv("T2SC_UNITS"); return e ? atoi(e) : 0; }();
+    if (force_u == 1) return args.Ci == KCH ? launch_p<BN, MH, 2, 1, false, T>(ctx, tm, args, max_items) : launch_p<BN, MH, 1, 1, false, T>(ctx, tm, args, max_items);
+#endif
+    return launch_p<BN, MH, 2, 2, false, T>(ctx, tm, args, max_items);
+  } else {
+    if constexpr (MH == 1) {
+      if (args.Ci == KCH) return launch_p<BN, MH, 2, 1, false, T>(ctx, tm, args, max_items);
+    }
+    return launch_p<BN, MH, 1, 1, false, T>(ctx, tm, args, max_items);
   }
-  return launch_p<BN, MH, 1, false, T>(ctx, tm, args, max_items);
 }
 
 template <int MH, class T>
@@ -452,14 +524,36 @@ int conv_umma_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const 
   if (cr != CUDA_SUCCESS) return t2sc_fail(ctx, T2SC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for weights [%lld,27,%d]", (int)cr, (long long)w_rows, Ci);
   ConvArgs args;
   diag_args(args);
+#ifdef T2SC_DIAG
+  static long long* trace_buf = nullptr;
+  const char* trace_path = getenv("T2SC_TRACE");
+  if (trace_path) {
+    if (!trace_buf) T2_CUDA(ctx, cudaMalloc(&trace_buf, 5 * 4 * 64 * sizeof(long long)));
+    T2_CUDA(ctx, cudaMemsetAsync(trace_buf, 0, 5 * 4 * 64 * sizeof(long long), ctx->stream));
+    args.trace = trace_buf;
+  }
+#endif
   args.n_in = (uint32_t)n_in;
   args.npeers = n_peers; args.self_rank = self_rank;
   for (int r = 0; r < 8; r++) { args.xp[r] = r < n_peers ? x_peers[r] : nullptr; args.xp_rows[r] = r < n_peers ? (uint32_t)rows_peers[r] : 0u; }
+  if (n_peers == 0) { int prc = plan_table_prepare(ctx, const_cast<t2sc_plan*>(plan), n_in); if (prc != T2SC_OK) return prc; }
+  args.tnbr = plan->tnbr;
   args.x = x; args.y = y; args.nbr = peer_nbr ? peer_nbr : plan->nbr; args.order = plan->order; args.src = plan->src;
   args.tiles = plan->tiles; args.tile_lo = tile_part(plan, part).lo; args.tile_hi = tile_part(plan, part).hi; args.status = ctx->status;
   args.Ci = Ci; args.Co = Co; args.n_cot = Co / BN; args.is_bf16 = dtype == T2SC_BF16; args.ep = ep;
   i64 max_items = plan->max_tiles * args.n_cot;
+  int rc;
   if (plan->tile_rows == 2 * TILE_M)
-    return dtype == T2SC_BF16 ? launch_t<2, __nv_bfloat16>(ctx, BN, tm, args, max_items) : launch_t<2, __half>(ctx, BN, tm, args, max_items);
-  return dtype == T2SC_BF16 ? launch_t<1, __nv_bfloat16>(ctx, BN, tm, args, max_items) : launch_t<1, __half>(ctx, BN, tm, args, max_items);
+    rc = dtype == T2SC_BF16 ? launch_t<2, __nv_bfloat16>(ctx, BN, tm, args, max_items) : launch_t<2, __half>(ctx, BN, tm, args, max_items);
+  else
+    rc = dtype == T2SC_BF16 ? launch_t<1, __nv_bfloat16>(ctx, BN, tm, args, max_items) : launch_t<1, __half>(ctx, BN, tm, args, max_items);
+#ifdef T2SC_DIAG
+  if (rc == T2SC_OK && args.trace) {        // every launch overwrites the file: the last launch of the process is what is kept
+    static long long host_trace[5 * 4 * 64];
+    T2_CUDA(ctx, cudaMemcpyAsync(host_trace, args.trace, sizeof(host_trace), cudaMemcpyDeviceToHost, ctx->stream));
+    T2_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (FILE* f = fopen(getenv("T2SC_TRACE"), "wb")) { fwrite(host_trace, 1, sizeof(host_trace), f); fclose(f); }
+  }
+#endif
+  return rc;
 }

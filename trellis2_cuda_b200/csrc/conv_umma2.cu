@@ -336,6 +336,7 @@ int conv_umma2_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (cr != CUDA_SUCCESS) return t2sc_fail(ctx, T2SC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)cr);
   ConvArgs args;
+  args.tnbr = nullptr;
   args.x = x; args.y = y; args.nbr = plan->nbr; args.order = plan->order; args.src = plan->src;
   args.tiles = plan->tiles; args.tile_lo = tile_part(plan, part).lo; args.tile_hi = tile_part(plan, part).hi; args.status = ctx->status;
   args.Ci = Ci; args.Co = Co; args.n_cot = Co / P_BN; args.is_bf16 = dtype == T2SC_BF16; args.ep = ep; args.npeers = 0;

@@ -93,7 +93,72 @@ __global__ void k_plan_tiles(const int* __restrict__ gray, const int* __restrict
   }
 }
 
+// The neighbour map in tile order: table[t][v][j] = entry of tap v of the j-th row of tile t (for a subdivision plan: of
+// that child's parent), 0x80000000 for an absent neighbour and for j past the tile's rows.  One CTA per tile; the rows
+// are read as they lie in the caller's map (27 consecutive words) and written tap-major through shared memory.
+constexpr uint32_t TABLE_ABSENT = 0x80000000u;
+template <int TILE>
+__global__ void __launch_bounds__(256) k_plan_table(const uint32_t* __restrict__ nbr, const int* __restrict__ src, const int* __restrict__ order,
+                                                    const PlanTile* __restrict__ tiles, const int* __restrict__ ntiles, uint32_t* __restrict__ table) {
+  const int t = blockIdx.x;
+  if (t >= *ntiles) return;
+  __shared__ int s_row[TILE];
+  __shared__ uint32_t s_e[27 * (TILE + 1)];
+  const PlanTile tile = tiles[t];
+  for (int j = threadIdx.x; j < TILE; j += 256) {
+    int nr = -1;
+    if (j < tile.rows) { const int r = order[tile.start + j]; nr = src ? (src[r] >> 3) : r; }
+    s_row[j] = nr;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < TILE * 27; e += 256) {
+    const int j = e / 27, v = e - j * 27, nr = s_row[j];
+    uint32_t val = TABLE_ABSENT;
+    if (nr >= 0) { val = __ldg(nbr + (i64)nr * 27 + v); if (val == NBR_EMPTY) val = TABLE_ABSENT; }
+    s_e[v * (TILE + 1) + j] = val;
+  }
+  __syncthreads();
+  uint32_t* out = table + (i64)t * 27 * TILE;
+  for (int e = threadIdx.x; e < TILE * 27; e += 256) {
+    const int v = e / TILE, j = e - v * TILE;
+    out[e] = s_e[v * (TILE + 1) + j];
+  }
+}
+
+// entries at or above n_in become absent and are reported (status bit 8)
+__global__ void k_plan_table_check(uint32_t* __restrict__ table, const int* __restrict__ ntiles, int per_tile, uint32_t n_in, int* status) {
+  const i64 n = (i64)*ntiles * per_tile;
+  bool bad = false;
+  for (i64 i = blockIdx.x * (i64)blockDim.x + threadIdx.x; i < n; i += (i64)gridDim.x * blockDim.x) {
+    const uint32_t e = table[i];
+    if (e != TABLE_ABSENT && e >= n_in) { table[i] = TABLE_ABSENT; bad = true; }
+  }
+  if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicOr(status, 256);
+}
+
+int plan_table_build(t2sc_ctx* ctx, t2sc_plan* p) {
+  if (p->n_out == 0) return T2SC_OK;
+  if (p->tile_rows == 128)
+    k_plan_table<128><<<(unsigned)p->max_tiles, 256, 0, ctx->stream>>>(p->nbr, p->src, p->order, p->tiles, p->ntiles, p->tnbr);
+  else
+    k_plan_table<256><<<(unsigned)p->max_tiles, 256, 0, ctx->stream>>>(p->nbr, p->src, p->order, p->tiles, p->ntiles, p->tnbr);
+  T2_LAUNCHED(ctx);
+  return T2SC_OK;
+}
+
 }  // namespace
+
+// Called by the conv launcher: the table holds no entry at or above n_in.  The check runs once per n_in; when n_in changes
+// after a check the table is rebuilt from the caller's map first, because the earlier check may have blanked entries
+// that are in range now.
+int plan_table_prepare(t2sc_ctx* ctx, t2sc_plan* p, i64 n_in) {
+  if (p->table_n_in == n_in || p->n_out == 0) return T2SC_OK;
+  if (p->table_n_in >= 0) { int rc = plan_table_build(ctx, p); if (rc != T2SC_OK) return rc; }
+  k_plan_table_check<<<2 * ctx->num_sms, 256, 0, ctx->stream>>>(p->tnbr, p->ntiles, 27 * p->tile_rows, (uint32_t)n_in, ctx->status);
+  T2_LAUNCHED(ctx);
+  p->table_n_in = n_in;
+  return T2SC_OK;
+}
 
 static int plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_t* gray, int64_t n_rows,
                        const int32_t* src, int64_t m, int64_t halo_from, int64_t block_rows, int tile_rows, t2sc_plan** out) {
@@ -124,6 +189,7 @@ static int plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_t* gray, 
 #define PL(call) do { if ((e = (call)) != cudaSuccess) return fail(e); } while (0)
   PL(t2_alloc(ctx, &p->order, (size_t)m));
   PL(t2_alloc(ctx, &p->tiles, (size_t)p->max_tiles));
+  PL(t2_alloc(ctx, &p->tnbr, (size_t)p->max_tiles * 27 * tile_rows));
   PL(t2_alloc(ctx, &p->bounds, 3));
   p->ntiles = p->bounds + 2;
   PL(t2_alloc(ctx, &p->stats, 2));
@@ -149,6 +215,7 @@ static int plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_t* gray, 
     ctx->launches++; PL(cudaGetLastError());
     k_plan_tiles<<<cdiv_i(p->max_tiles * 32, 256), 256, 0, ctx->stream>>>(gray, src, p->order, gmeta, ngroups, split, TILE, p->ntiles, p->tiles, p->stats);
     ctx->launches++; PL(cudaGetLastError());
+    if (plan_table_build(ctx, p) != T2SC_OK) return fail(cudaGetLastError());
   }
 #undef PL
   t2_free(ctx, keys); t2_free(ctx, keys2); t2_free(ctx, iota); t2_free(ctx, gcnt); t2_free(ctx, gmeta); t2_free(ctx, tmp);
@@ -189,7 +256,7 @@ extern "C" int t2sc_plan_destroy(t2sc_ctx* ctx, t2sc_plan* p) {
   if (!p) return T2SC_OK;
   T2_REQ(ctx, ctx != nullptr, "null context");
   cudaSetDevice(ctx->device);
-  t2_free(ctx, p->order); t2_free(ctx, p->tiles); t2_free(ctx, p->bounds); t2_free(ctx, p->stats);
+  t2_free(ctx, p->order); t2_free(ctx, p->tiles); t2_free(ctx, p->tnbr); t2_free(ctx, p->bounds); t2_free(ctx, p->stats);
   delete p;
   return T2SC_OK;
 }

@@ -53,12 +53,14 @@ __host__ __device__ constexpr int num_acc_bufs(int BN, int MH) { return 2 * MH *
 
 struct ConvArgs {
   const void* x; void* y; const uint32_t* nbr; const int* order; const int* src;
+  const uint32_t* tnbr;     // the plan's map in tile order, [tile][27][rows]: one bulk copy per tile (not in the peer-memory form)
   const PlanTile* tiles; const int* tile_lo; const int* tile_hi; int* status;      // this launch covers tiles [*tile_lo, *tile_hi)
   int Ci, Co, n_cot, is_bf16;
   int npeers, self_rank;    // npeers > 0: map entries are (owner << PEER_SHIFT) | row and rows are read from xp[owner]; xp[self_rank] is local
   const void* xp[8];
   uint32_t n_in;            // rows of x (PEERS: unused, see xp_rows); a map entry at or above it is reported and read as absent
   uint32_t xp_rows[8];      // PEERS: rows of every peer's array
+  long long* trace;         // diagnostic build only (T2SC_TRACE=file): per-tile timestamps of CTA 0's roles, [role][event][tile < 64]
   int wait_limit;           // bounded waits give up after this many cycles >> WAIT_LIMIT_SHIFT
   int dbg_skip;             // diagnostic build only (T2SC_DEBUG_SKIP), always 0 in the shipped library: 1 = no A gather, 2 = no B load,
                             // 4 = no MMA, 8 = CTA 0 prints where each role waited, 16 = the weight lane never signals its first stage,
@@ -67,10 +69,16 @@ struct ConvArgs {
 };
 
 __device__ __forceinline__ bool diag(const ConvArgs& a, int bits) { return kDiag && (a.dbg_skip & bits) != 0; }
+// diagnostic build: timestamp of event `ev` (0..3) of role `role` (0 gather, 1 weights, 2 index, 3 MMA, 4 epilogue) at the
+// CTA's `tile`-th tile, CTA 0 only
+__device__ __forceinline__ void trace(const ConvArgs& a, int role, int ev, uint32_t tile) {
+  if (kDiag && a.trace && blockIdx.x == 0 && tile < 64) a.trace[(role * 4 + ev) * 64 + tile] = clock64();
+}
 // Host side: the shipped library always runs with no switch set and the full wait limit; the diagnostic build reads
 // T2SC_DEBUG_SKIP (bit mask above) and T2SC_WAIT_LIMIT_CYCLES from the environment.
 static inline void diag_args(ConvArgs& args) {
   args.dbg_skip = 0;
+  args.trace = nullptr;
   args.wait_limit = (int)(WAIT_LIMIT_CYCLES >> WAIT_LIMIT_SHIFT);
 #ifdef T2SC_DIAG
   static const int dbg_skip = [] { const char* e = getenv("T2SC_DEBUG_SKIP"); return e ? atoi(e) : 0; }();
@@ -117,7 +125,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   const long long t0 = clock64();
   for (;;) {
     if (abort_flag[0] || clock64() - t0 > ((long long)abort_flag[1] << WAIT_LIMIT_SHIFT)) { abort_flag[0] = 1; atomicOr(status, code); return false; }
+#if T2SC_WAIT_HINT_NS > 0
     if (mbar_try_sleep(bar, parity)) return true;
+#else
+    if (mbar_try(bar, parity)) return true;
+#endif
   }
 }
 // diagnostic build: waits that also add their duration to a per-role counter
@@ -143,6 +155,11 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// untiled bulk copy global -> shared, completion counted in bytes on `bar`; addresses and size multiples of 16
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm, int c0, int c1, int c2, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
                ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
@@ -154,6 +171,23 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
 }
 __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The four K = 16 MMAs of one 64-channel unit as ONE instruction block: the operand descriptors of steps 1..3 are the
+// step-0 descriptors + 32, 64, 96 bytes along K (+2, +4, +6 in the address field, which sits in the low word and cannot
+// carry out of it), only step 0 can be the tile's first MMA (accumulate = 0 overwrites the accumulator).  The MMA lane
+// runs about one instruction per ten clocks, so the descriptor arithmetic is kept to one add per operand and step.
+__device__ __forceinline__ void tc_mma_k64(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p, t;\n\t.reg .b32 al, ah, bl, bh, x;\n\t.reg .b64 a, b;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\tsetp.eq.b32 t, %4, %4;\n\t"
+               "mov.b64 {al, ah}, %1;\n\tmov.b64 {bl, bh}, %2;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+               "add.u32 x, al, 2;\n\tmov.b64 a, {x, ah};\n\tadd.u32 x, bl, 2;\n\tmov.b64 b, {x, bh};\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, t;\n\t"
+               "add.u32 x, al, 4;\n\tmov.b64 a, {x, ah};\n\tadd.u32 x, bl, 4;\n\tmov.b64 b, {x, bh};\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, t;\n\t"
+               "add.u32 x, al, 6;\n\tmov.b64 a, {x, ah};\n\tadd.u32 x, bl, 6;\n\tmov.b64 b, {x, bh};\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, t;\n\t}"
                ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {

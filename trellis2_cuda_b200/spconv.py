@@ -162,12 +162,16 @@ class SpConvCache:
     def plan(self) -> _Plan:
         return self.plan_for(256)
 
+    def _tile_rows_for(self, Co: int, Ci: int) -> int:
+        """128-row tiles unless forced: every layer narrower than 256 output channels runs the form of the kernel that packs
+        several (tap, chunk) units into one pipeline stage, which exists for 128-row tiles; 256-channel slabs share nothing
+        between two 128-row halves that the L2 does not already give them (measured on 218 k rows: 256-row tiles are 10 %
+        slower there because one union mask then covers 256 rows)."""
+        return self._tile_rows or 128
+
     def plan_for(self, Co: int, Ci: int = 0) -> _Plan:
-        """The schedule used for a conv with Ci -> Co channels, unless tile_rows was forced: 128-row tiles, except 256-row
-        tiles (two accumulators per weight slab) for layers of 128 input channels on maps too large for the L2 (measured:
-        8.6 M rows at C = 128 run 3 % faster with them; 218 k rows run 10 % slower; at 64 input channels 128-row tiles
-        with two gather groups are the fastest at every size)."""
-        tr = self._tile_rows or (256 if (self.N > (1 << 18) and Co < 256 and Ci != 64) else 128)
+        """The schedule used for a conv with Ci -> Co channels."""
+        tr = self._tile_rows_for(Co, Ci)
         if self._plan is None:
             self._plan = {}
         if tr not in self._plan:
@@ -177,7 +181,7 @@ class SpConvCache:
     def split_plan_for(self, Co: int, Ci: int, n_own: int) -> _Plan:
         """The schedule of one rank of a partitioned scene whose map indexes owned rows (< n_own) and appended halo rows:
         same tile height as :meth:`plan_for`, interior tiles first, boundary tiles last (see :func:`subm_conv_split`)."""
-        tr = self._tile_rows or (256 if (self.N > (1 << 18) and Co < 256 and Ci != 64) else 128)
+        tr = self._tile_rows_for(Co, Ci)
         if self._plan is None:
             self._plan = {}
         if ("split", tr, n_own) not in self._plan:
@@ -337,13 +341,22 @@ class Level:
     src: Optional[torch.Tensor]
     nb: SpConvCache
     parent: Optional[SpConvCache] = None
-    _up_plan: Optional[_Plan] = None
+    _up_plans: Optional[dict] = None
+
+    def up_plan_for(self, Cc: int) -> _Plan:
+        """Schedule of the subdivision conv into Cc child channels: 256-row tiles (two 128-row accumulators per weight
+        slab) for 256-column slabs, 128-row tiles below, where the several-units-per-stage form of the kernel runs."""
+        tr = 256 if Cc % 256 == 0 else 128
+        if self._up_plans is None:
+            self._up_plans = {}
+        if tr not in self._up_plans:
+            self._up_plans[tr] = _Plan(self.parent.ctx, self.parent.nbr, self.parent.gray, self.src, 0, tr)
+        return self._up_plans[tr]
 
     @property
     def up_plan(self) -> _Plan:
-        if self._up_plan is None:
-            self._up_plan = _Plan(self.parent.ctx, self.parent.nbr, self.parent.gray, self.src, 0, 256)
-        return self._up_plan
+        """The subdivision schedule made last (for inspection)."""
+        return self.up_plan_for(256) if not self._up_plans else list(self._up_plans.values())[-1]
 
 
 def subdivide(parent: SpConvCache, sub: torch.Tensor, want_sorted: bool = False) -> Level:
@@ -374,7 +387,7 @@ def subdiv_conv(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], lev
         raise T2scError(-1, "subdivision conv needs 8*Cc weight rows")
     if x.shape[0] != level.parent.N:
         raise T2scError(-1, f"spconv shapes: x has {x.shape[0]} rows, parent cache has {level.parent.N}")
-    return _conv(level.parent.ctx, level.up_plan, x, w, b, w.shape[0] // 8, ln, act, None, None, variant, out)
+    return _conv(level.parent.ctx, level.up_plan_for(w.shape[0] // 8), x, w, b, w.shape[0] // 8, ln, act, None, None, variant, out)
 
 
 def gather_rows(x: torch.Tensor, src: torch.Tensor, C: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
