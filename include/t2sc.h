@@ -157,7 +157,9 @@ typedef struct {
 int t2sc_subm_conv(t2sc_ctx* ctx, t2sc_plan* plan, const void* x, const void* w, const t2sc_epilogue* ep,
                    void* y, int dtype, int64_t n_in, int Ci, int Co, int variant);
 
-/* t2sc_subm_conv over one part of a plan (T2SC_PART_*): the rows of the other part are left untouched in y. */
+/* t2sc_subm_conv over one part of a plan (T2SC_PART_*): the rows of the other part are left untouched in y.  n_in is the
+ * index space of the plan's map as for t2sc_subm_conv; T2SC_PART_INTERIOR of a split plan reads rows below n_own only, so
+ * x may end there (a rank whose boundary tiles gather the halo rows from peer memory never copies them). */
 int t2sc_subm_conv_part(t2sc_ctx* ctx, t2sc_plan* plan, const void* x, const void* w, const t2sc_epilogue* ep,
                         void* y, int dtype, int64_t n_in, int Ci, int Co, int variant, int part);
 

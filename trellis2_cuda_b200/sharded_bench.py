@@ -76,7 +76,8 @@ def measure(args, rank, world, local_rank, peaks, ClockSampler, visible_gpu_inde
     parts = split.parts() if split is not None else {"interior_tiles": st["tiles"], "boundary_tiles": 0}
     sync(); setup["schedule_ms"] = (time.perf_counter() - t0) * 1e3
 
-    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    g = torch.Generator(device=dev).manual_seed(1234)
+    x_full = torch.randn((N, C), generator=g, device=dev).to(td)       # the same on every rank: the one-GPU check needs the whole input
     if p2p:
         import torch.distributed._symmetric_memory as symm
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")      # plain peer loads only
@@ -94,7 +95,9 @@ def measure(args, rank, world, local_rank, peaks, ClockSampler, visible_gpu_inde
     else:
         xa = torch.zeros((plan.n_local, C), dtype=td, device=dev)
         xb = torch.zeros((plan.n_local, C), dtype=td, device=dev)
-    x0 = torch.randn((plan.n_own, C), generator=g, device=dev).to(td)
+    x0 = x_full[lo:hi].clone()
+    if rank != 0:
+        del x_full
     ws = [torch.from_numpy(scenes.kaiming_uniform_weight(C, C, 100 + l)).to(dev).to(td) for l in range(layers)]
     send_buf = torch.empty((max(int(plan.send_idx.numel()), 1), C), dtype=td, device=dev)
     epoch = [0]
@@ -113,7 +116,7 @@ def measure(args, rank, world, local_rank, peaks, ClockSampler, visible_gpu_inde
                 sp.peer_barrier(ctx, flag_ptrs, rank, epoch[0])
                 if timers:
                     timers[1][l].record()
-                sp.subm_conv_split(a, ws[l], None, cache, split, "interior", out=b[:plan.n_own])
+                sp.subm_conv_split(a, ws[l], None, cache, split, "interior", out=b[:plan.n_own], n_local=plan.n_local)
                 sp.subm_conv_peers(ptrs[a.data_ptr()], rows_of, rank, td, C, ws[l], None, cache, out=b[:plan.n_own],
                                    plan=split, part="boundary", peer_nbr=peer_nbr)
             else:
@@ -186,19 +189,26 @@ def measure(args, rank, world, local_rank, peaks, ClockSampler, visible_gpu_inde
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
         dist.all_reduce(sums, op=dist.ReduceOp.SUM)
 
-    single = None
-    if single_gpu_steps > 0 and world > 1:
-        # the same scene on ONE GPU, measured on rank 0 in this run (the other ranks wait at the barrier below)
-        del xa, xb
+    single, verified = None, None
+    if world > 1:
+        # The same scene on ONE GPU, on rank 0 in this run (the other ranks wait at the barrier below): its time, and the
+        # check that the sharded result equals it bit for bit (every output row sums its taps in the same order however the
+        # rows are tiled or sharded).
+        rows_max = max(starts[r + 1] - starts[r] for r in range(world))
+        mine = torch.zeros((rows_max, C), dtype=td, device=dev)
+        mine[:plan.n_own].copy_(step()[:plan.n_own])
+        parts_out = [torch.empty_like(mine) for _ in range(world)] if rank == 0 else None
+        dist.gather(mine, parts_out, dst=0)
+        del xa, xb, mine
         if rank == 0:
             full = sp.build_neighbors(coords, want_sorted=False)
-            xa1 = torch.randn((N, C), generator=g, device=dev).to(td)
-            xb1 = torch.empty_like(xa1)
+            xa1, xb1 = x_full.clone(), torch.empty_like(x_full)
             ms1 = []
-            for i in range(single_gpu_steps + 1):
+            for i in range(max(single_gpu_steps, 1) + 1):
                 s, e = ev(), ev()
                 s.record()
                 a, b = xa1, xb1
+                a.copy_(x_full)
                 for l in range(layers):
                     sp.subm_conv(a, ws[l], None, full, out=b)
                     a, b = b, a
@@ -208,7 +218,8 @@ def measure(args, rank, world, local_rank, peaks, ClockSampler, visible_gpu_inde
                     ms1.append(s.elapsed_time(e))
             single = sum(ms1) / len(ms1)
             ctx.device_status()
-            del full, xa1, xb1
+            verified = all(torch.equal(parts_out[r][:starts[r + 1] - starts[r]], a[starts[r]:starts[r + 1]]) for r in range(world))
+            del full, xa1, xb1, parts_out
         dist.barrier()
     if rank != 0:
         return None
@@ -239,6 +250,7 @@ def measure(args, rank, world, local_rank, peaks, ClockSampler, visible_gpu_inde
     if single is not None:
         block["single_gpu_ms_per_step"] = single
         block["speedup_vs_single_gpu"] = single / ms
+        block["equals_single_gpu_result_bit_for_bit"] = verified
     if e2e:
         block["e2e"] = {"value": flops / (vals[2].item() * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": N * C * es, "d2h_bytes_per_step": N * C * es,
                         "ms_per_step": vals[2].item(), "path": "owned features from pinned host memory in, 4 layers, final features to pinned host memory"}
@@ -263,4 +275,7 @@ def run(args, rank, world, local_rank, METRIC, peaks, ClockSampler, visible_gpu_
                          "frac": b["per_gpu_frac_of_sustained_peak"], "traffic": None,
                          "peak_source": f"{pk_src} cuBLAS bf16 sustained (kernel timed inside a multi-ms step)", "kernel": "k_conv_umma", "per": "GPU"},
             "clocks": b["clocks"], "gpu_launches": b["gpu_launches"], "e2e": b.get("e2e")}
+    for k in ("single_gpu_ms_per_step", "speedup_vs_single_gpu", "equals_single_gpu_result_bit_for_bit"):
+        if k in b:
+            line[k] = b[k]
     print(json.dumps(line), flush=True)

@@ -231,22 +231,27 @@ def subm_conv_local(x: torch.Tensor, w: torch.Tensor, b, c: SpConvCache, **kw) -
 
 
 def subm_conv_split(x: torch.Tensor, w: torch.Tensor, b, c: SpConvCache, plan: _Plan, part: str, *, ln=None, act=None,
-                    residual=None, out=None) -> torch.Tensor:
+                    residual=None, out=None, n_local: Optional[int] = None) -> torch.Tensor:
     """One part ("interior" | "boundary" | "all") of a conv over a split plan (:meth:`SpConvCache.split_plan_for`): x has
     the owned rows first and the halo rows appended; the interior part reads owned rows only, so it can run while the
     halo rows are still in flight.  Both parts write into the same `out` [c.N, Co]; the rows of the other part are left
-    untouched."""
+    untouched.  `n_local` (owned + halo rows, the index space of the plan's map) may be given when x itself holds fewer rows
+    - the interior part of a rank whose halo rows are never copied because its boundary tiles gather them from peer
+    memory."""
     if x.shape[0] < c.N:
         raise T2scError(-1, f"spconv shapes: x has {x.shape[0]} rows, cache has {c.N}")
+    if n_local is not None and part != "interior":
+        raise T2scError(-1, "n_local may exceed the rows of x only for the interior part, which reads owned rows alone")
     _chk(x, "x", None, 2); _chk(w, "w", x.dtype, 3)
     Ci, Co = x.shape[1], w.shape[0]
     if w.shape[1] != 27 or w.shape[2] != Ci:
         raise T2scError(-1, f"spconv shapes: w {tuple(w.shape)} does not match x {tuple(x.shape)}")
-    plan.set_input_rows(x.shape[0])
+    n_in = x.shape[0] if n_local is None else n_local
+    plan.set_input_rows(n_in)
     y = out if out is not None else torch.empty((plan.n_out, Co), dtype=x.dtype, device=x.device)
     e, keep = _epilogue(Co, x.dtype, b, ln, act, residual, None)
     plan.keep = keep
-    c.ctx.check(c.ctx.lib.t2sc_subm_conv_part(c.ctx.h, plan.h, _ptr(x), _ptr(w), ctypes.byref(e), _ptr(y), _DT[x.dtype], x.shape[0], Ci, Co,
+    c.ctx.check(c.ctx.lib.t2sc_subm_conv_part(c.ctx.h, plan.h, _ptr(x), _ptr(w), ctypes.byref(e), _ptr(y), _DT[x.dtype], n_in, Ci, Co,
                                               0, _lib.PART[part]))
     return y
 
