@@ -243,6 +243,8 @@ def run_single_conv(args, rank, world, local_rank, dev):
     from trellis2_cuda_b200 import scenes
 
     wl = make_workload(args.workload, 0)               # the same scene on every rank
+    if args.channels:                                  # the same geometry at another width (the narrow-layer rows of the result tables)
+        wl.update(Ci=args.channels, Co=args.channels, desc=wl["desc"] + f" [geometry only: run at {args.channels}->{args.channels} channels]")
     td = TD[wl["dtype"]]
     coords_h = torch.from_numpy(wl["coords"]).pin_memory()
     n, Ci, Co = coords_h.shape[0], wl["Ci"], wl["Co"]
@@ -257,7 +259,7 @@ def run_single_conv(args, rank, world, local_rank, dev):
 
     def step(record=None):
         cache = sp.build_neighbors(coords, want_sorted=False)
-        _ = cache.plan_for(Co, Ci)                        # the schedule this conv will use (tile height depends on Co and N)
+        cache.plan_for(Co, Ci).check(n)                   # the schedule this conv will use, its map copy checked against the n feature rows
         if record:
             record[0].record()
         y = sp.subm_conv(x, w, None, cache)
@@ -360,7 +362,7 @@ def run_single_conv(args, rank, world, local_rank, dev):
     traffic = None
     tp = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(tp):
-        traffic = json.load(open(tp)).get(f"{args.workload}_conv_dram_bytes_per_launch")
+        traffic = json.load(open(tp)).get(f"{args.workload}_conv_dram_bytes_per_launch") if not args.channels else None
     if tensor_bound:
         roof = {"bound": "tensor", "achieved": achieved, "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / pk["bf16_tflops"], "traffic": traffic,
                 "peak_source": f"{pk_src} cuBLAS bf16 burst (kernel timed alone, L2 flushed between steps)", "kernel": "k_conv_umma",
@@ -425,7 +427,7 @@ def run_cfg3(args, rank, world, local_rank, dev):
         mark(1)
         lv = sp.subdivide(parent, flags)
         mark(2)
-        _ = lv.up_plan_for(Cc), lv.nb.plan_for(Cc, Cc)
+        lv.up_plan_for(Cc).check(n); lv.nb.plan_for(Cc, Cc).check(lv.coords.shape[0])
         mark(3)
         up = sp.subdiv_conv(x, w1, None, lv)
         mark(4)
@@ -634,6 +636,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"])
     ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--channels", type=int, default=0, help="cfg1/cfg2: run the workload's geometry at this channel width instead of its own")
     ap.add_argument("--halo", default="nccl", choices=["p2p", "nccl"], help="cfg5: halo rows by peer-memory loads inside the conv, or by NCCL all-to-all")
     ap.add_argument("--profile", action="store_true", help="timed steps only (no sustained / end-to-end leg, no baselines): for runs under ncu")
     ap.add_argument("--no-sharded", action="store_true", help="N > 1: leave out the sharded cfg5 block")

@@ -61,6 +61,14 @@ int t2sc_build_neighbors(t2sc_ctx* ctx, const int32_t* coords, int64_t n, int W,
 int t2sc_build_neighbors_range(t2sc_ctx* ctx, const int32_t* coords, int64_t n, int W, int H, int D,
                                int64_t row_lo, int64_t row_hi, uint32_t* nbr, int32_t* gray);
 
+/* Rows of arbitrary coordinates: rows[q] = index of the row of coords [n,4] equal to queries[q] = (b,x,y,z), or 0xffffffff
+ * (also for a query outside [0,W)x[0,H)x[0,D) or with a negative batch index).  The lookup the reference's other users
+ * of a voxel hash need: vhash_find (src/mesh.cu:7-19), which the dual-grid quad search calls per edge (src/mesh.cu:54-72),
+ * and the hash half of the grid-sample neighbour build (src/glb.cu:545-552).  Same table and duplicate rule (lowest row
+ * index) as t2sc_build_neighbors; queries int32 [m,4], 16-byte aligned. */
+int t2sc_voxel_lookup(t2sc_ctx* ctx, const int32_t* coords, int64_t n, int W, int H, int D,
+                      const int32_t* queries, int64_t m, uint32_t* rows);
+
 /* Neighbour maps for callers that must not allocate.  (No counterpart in the reference, whose
  * build_neighbors always allocates.)  Same nbr / gray results as t2sc_build_neighbors, but the hash table is
  * a fixed 2 MiB array that is part of the library image, so this call performs no cudaMalloc, cudaFree or
@@ -115,6 +123,11 @@ int t2sc_plan_destroy(t2sc_ctx* ctx, t2sc_plan* plan);
  * partitioned scene: owned rows first, the halo rows of its peers appended).  Without it n_in == n_rows, which is what
  * the reference requires of subm_conv (REQ N == c.N, src/spconv.cu:162). */
 int t2sc_plan_set_input_rows(t2sc_ctx* ctx, t2sc_plan* plan, int64_t n_in);
+/* The plan keeps its own copy of the map in tile order (what the tcgen05 kernel reads; later changes to nbr are not seen by
+ * it).  Its entries are checked against the rows of the feature array once per n_in: entries at or above n_in are made
+ * absent and reported by t2sc_device_status.  The first conv with a given n_in does that; this call does it ahead of time,
+ * so that the conv launches nothing but the conv. */
+int t2sc_plan_check(t2sc_ctx* ctx, t2sc_plan* plan, int64_t n_in);
 /* Plan for one rank of a partitioned scene (no counterpart in the reference, which is single-GPU).  nbr is the rank's
  * LOCAL map over its n_rows owned rows: entries below n_own are owned rows, entries from n_own up are halo rows of its
  * peers appended behind them.  Rows none of whose taps reads a halo row form the interior part of the plan, the others

@@ -99,6 +99,29 @@ def test_neighbors_duplicates_lowest_index(sp):
     assert host(cache.nbr)[2, 13] == 0 and host(cache.nbr)[3, 13] == 1
 
 
+def test_voxel_lookup_finds_rows_of_arbitrary_coordinates(sp):
+    """The lookup the reference's mesh extraction does per edge (vhash_find, src/mesh.cu:14-19): present voxels give their
+    row, anything else -1: neighbours that do not exist, coordinates outside the grid, another batch item, duplicates
+    (lowest row wins, as in the neighbour map)."""
+    rng = np.random.default_rng(12)
+    c = random_coords(rng, 4000, 20, 2)
+    c = np.concatenate([c, c[:7]], 0)                                  # seven duplicated voxels at the end
+    where = {}
+    for i, row in enumerate(map(tuple, c)):
+        where.setdefault(row, i)
+    q = np.concatenate([c[rng.integers(0, len(c), 3000)], random_coords(rng, 3000, 22, 3),
+                        np.array([[0, -1, 0, 0], [0, 0, 20, 0], [-1, 1, 1, 1], [0, 19, 19, 19]], np.int32)], 0).astype(np.int32)
+    want = np.array([where.get(tuple(r), -1) if (0 <= r[1] < 20 and 0 <= r[2] < 20 and 0 <= r[3] < 20 and r[0] >= 0) else -1 for r in q], np.int32)
+    got = host(sp.voxel_lookup(dev(c), dev(q), 20, 20, 20))
+    assert np.array_equal(got, want) and (want >= 0).sum() > 3000 and (want < 0).sum() > 1000
+    # consistent with the neighbour map: the row found at coords + offset(v) is nbr[:, v]
+    cache = sp.build_neighbors(dev(c[:4000]), 20, 20, 20, want_sorted=False)
+    v = 5
+    off = np.array([0, v // 9 - 1, (v // 3) % 3 - 1, v % 3 - 1], np.int32)
+    assert np.array_equal(host(sp.voxel_lookup(dev(c[:4000]), dev(c[:4000] + off), 20, 20, 20)), host(cache.nbr)[:, v])
+    assert sp.voxel_lookup(dev(c), torch.zeros((0, 4), dtype=torch.int32, device="cuda")).shape == (0,)
+
+
 def test_subdivide_bit_exact(sp):
     rng = np.random.default_rng(5)
     c = random_coords(rng, 300, 8, 2)

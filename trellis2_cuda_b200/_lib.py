@@ -39,6 +39,7 @@ SYMBOLS = [
     ("t2sc_device_status", _i32, [_vp, _pi32]),
     ("t2sc_build_neighbors", _i32, [_vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp]),
     ("t2sc_build_neighbors_range", _i32, [_vp, _vp, _i64, _i32, _i32, _i32, _i64, _i64, _vp, _vp]),
+    ("t2sc_voxel_lookup", _i32, [_vp, _vp, _i64, _i32, _i32, _i32, _vp, _i64, _vp]),
     ("t2sc_build_neighbors_static", _i32, [_vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp]),
     ("t2sc_valid_taps", _i32, [_vp, _vp, _vp, _i64, _i32, _vp, _vp, _pi64]),
     ("t2sc_subdivide_count", _i32, [_vp, _vp, _i32, _i64, _vp, _pi64]),
@@ -50,6 +51,7 @@ SYMBOLS = [
     ("t2sc_plan_parts", _i32, [_vp, _vp, _pi64, _pi64]),
     ("t2sc_plan_destroy", _i32, [_vp, _vp]),
     ("t2sc_plan_set_input_rows", _i32, [_vp, _vp, _i64]),
+    ("t2sc_plan_check", _i32, [_vp, _vp, _i64]),
     ("t2sc_plan_stats", _i32, [_vp, _vp, _pi64, _pi64, _pi64]),
     ("t2sc_plan_order", _i32, [_vp, _vp, _vp]),
     ("t2sc_subm_conv", _i32, [_vp, _vp, _vp, _vp, ctypes.POINTER(Epilogue), _vp, _i32, _i64, _i32, _i32, _i32]),

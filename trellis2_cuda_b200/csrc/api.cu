@@ -54,6 +54,8 @@ extern "C" int t2sc_ctx_destroy(t2sc_ctx* ctx) {
   if (!ctx) return T2SC_OK;
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
+  if (ctx->arena) cudaFreeAsync(ctx->arena, ctx->stream);
+  cudaStreamSynchronize(ctx->stream);
   cudaFree(ctx->status);
   if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
   delete ctx;

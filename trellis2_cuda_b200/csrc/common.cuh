@@ -19,6 +19,8 @@ struct t2sc_ctx {
   int num_sms = 148;
   int smem_optin = 0;
   i64 launches = 0;
+  char* arena = nullptr;        // scratch arena of the entry points (see Scratch), arena_bytes long; grown to arena_want
+  size_t arena_bytes = 0, arena_want = 0;
   int* status = nullptr;        // device word; kernels OR an error code into it when a bounded wait gives up
   char err[1024] = {0};
 };
@@ -38,7 +40,8 @@ struct t2sc_plan {
                                 // CTA copies into shared memory with one bulk copy)
   i64 table_n_in = -1;          // n_in the table was last checked against (-1: not yet)
   PlanTile* tiles = nullptr;    // [max_tiles]
-  int* bounds = nullptr;        // device [3]: {0, first boundary tile, realised tile count}; parts are [b0,b1) and [b1,b2)
+  int* meta = nullptr;          // device [16]: group counts, bounds, stats (one allocation, one memset)
+  int* bounds = nullptr;        // = meta + 8, device [3]: {0, first boundary tile, realised tile count}; parts are [b0,b1) and [b1,b2)
   int* ntiles = nullptr;        // = bounds + 2: realised tile count (<= max_tiles)
   bool split = false;           // made by t2sc_plan_create_split: interior tiles first, boundary tiles last
   unsigned long long* stats = nullptr;  // device [2]: computed taps, active taps
@@ -68,19 +71,35 @@ template <class T> static inline cudaError_t t2_alloc(t2sc_ctx* ctx, T** p, size
   return cudaMallocAsync((void**)p, (count ? count : 1) * sizeof(T), ctx->stream);
 }
 static inline void t2_free(t2sc_ctx* ctx, void* p) { if (p) cudaFreeAsync(p, ctx->stream); }
-// Scratch of one entry point: everything taken through it goes back to the pool (stream-ordered) when the entry point
-// returns, on the error paths too.
+// Scratch of one entry point.  Steady state takes nothing from the memory pool: the context keeps one arena (grown to the
+// largest total any call has needed) and a call carves its pieces out of it in order; calls on a context run one after the
+// other on its stream, so the next call may overwrite what this one used.  A request the arena cannot hold falls back to
+// the stream-ordered pool (returned when the entry point returns, on the error paths too) and raises the size the arena
+// is grown to before the next call.
 struct Scratch {
-  t2sc_ctx* ctx; void* held[16]; int n = 0;
-  explicit Scratch(t2sc_ctx* c) : ctx(c) {}
+  t2sc_ctx* ctx; void* held[16]; int n = 0; size_t used = 0, wanted = 0;
+  explicit Scratch(t2sc_ctx* c) : ctx(c) {
+    if (c->arena_want > c->arena_bytes) {
+      if (c->arena) cudaFreeAsync(c->arena, c->stream);
+      c->arena = nullptr; c->arena_bytes = 0;
+      if (cudaMallocAsync((void**)&c->arena, c->arena_want, c->stream) == cudaSuccess) c->arena_bytes = c->arena_want;
+      else (void)cudaGetLastError();
+    }
+  }
   Scratch(const Scratch&) = delete;
   Scratch& operator=(const Scratch&) = delete;
   template <class T> cudaError_t get(T** p, size_t count) {
-    cudaError_t e = n < 16 ? t2_alloc(ctx, p, count) : cudaErrorMemoryAllocation;
+    const size_t bytes = (((count ? count : 1) * sizeof(T)) + 255) & ~(size_t)255;
+    wanted += bytes;
+    if (used + bytes <= ctx->arena_bytes) { *p = (T*)(ctx->arena + used); used += bytes; return cudaSuccess; }
+    cudaError_t e = n < 16 ? cudaMallocAsync((void**)p, bytes, ctx->stream) : cudaErrorMemoryAllocation;
     if (e == cudaSuccess) held[n++] = (void*)*p;
     return e;
   }
-  ~Scratch() { for (int i = 0; i < n; i++) t2_free(ctx, held[i]); }
+  ~Scratch() {
+    for (int i = 0; i < n; i++) t2_free(ctx, held[i]);
+    if (wanted > ctx->arena_want) ctx->arena_want = wanted;
+  }
 };
 
 // ---- storage types: load as float, round float to storage and widen back

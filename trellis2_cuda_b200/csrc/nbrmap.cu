@@ -149,6 +149,25 @@ __global__ void __launch_bounds__(256) k_brick_neighbors(const int4* __restrict_
   }
 }
 
+// one thread per query coordinate: the row of the voxel that sits there, or NBR_EMPTY
+__global__ void k_brick_lookup(const int4* __restrict__ queries, i64 m, int W, int H, int D, int Wb, int Hb, int Db,
+                               const unsigned long long* __restrict__ keys, const BrickVals* __restrict__ vals, uint32_t mask,
+                               uint32_t* __restrict__ rows) {
+  const i64 i = blockIdx.x * (i64)blockDim.x + threadIdx.x;
+  if (i >= m) return;
+  const int4 q = queries[i];
+  uint32_t r = NBR_EMPTY;
+  if (q.x >= 0 && q.y >= 0 && q.y < W && q.z >= 0 && q.z < H && q.w >= 0 && q.w < D) {
+    const unsigned long long k = brick_key(q.x, q.y >> 1, q.z >> 1, q.w >> 1, Wb, Hb, Db);
+    for (uint32_t s = mix32(k) & mask, it = 0; it <= mask; s = (s + 1) & mask, ++it) {
+      const unsigned long long sk = __ldg(keys + s);
+      if (sk == KEY_EMPTY) break;
+      if (sk == k) { r = __ldg(&vals[s].v[(q.y & 1) | ((q.z & 1) << 1) | ((q.w & 1) << 2)]); break; }
+    }
+  }
+  rows[i] = r;
+}
+
 __global__ void k_iota(int* p, int n) { int i = blockIdx.x * blockDim.x + threadIdx.x; if (i < n) p[i] = i; }
 
 // ---- valid(B1): one warp per block of B1 sorted rows
@@ -409,6 +428,35 @@ extern "C" int t2sc_build_neighbors_range(t2sc_ctx* ctx, const int32_t* coords, 
   T2_LAUNCHED(ctx);
   const i64 m = row_hi - row_lo;
   k_brick_neighbors<<<cdiv_i(m, 32), 256, 0, ctx->stream>>>((const int4*)coords + row_lo, (int)m, W, H, D, Wb, Hb, Db, bkeys, bvals, cap - 1, nbr, gray, nullptr);
+  T2_LAUNCHED(ctx);
+  return T2SC_OK;
+}
+
+// Rows of arbitrary query coordinates in the same voxel hash: what the reference's other hash users need of it
+// (vhash_find of src/mesh.cu:7-19, used by the dual-grid quad search :54-72, and the hash half of the grid-sample
+// neighbour build, src/glb.cu:545-552).
+extern "C" int t2sc_voxel_lookup(t2sc_ctx* ctx, const int32_t* coords, int64_t n, int W, int H, int D,
+                                 const int32_t* queries, int64_t m, uint32_t* rows) {
+  T2_REQ(ctx, ctx != nullptr, "null context");
+  T2_REQ(ctx, n >= 0 && n < (1ll << 30) && m >= 0, "n=%lld m=%lld", (long long)n, (long long)m);
+  if (m == 0) return T2SC_OK;
+  T2_REQ(ctx, queries && rows && (n == 0 || coords), "null tensor");
+  T2_REQ(ctx, (uintptr_t)coords % 16 == 0 && (uintptr_t)queries % 16 == 0, "coords and queries must be 16-byte aligned");
+  T2_REQ(ctx, W > 0 && H > 0 && D > 0, "grid extent %d %d %d", W, H, D);
+  T2_CUDA(ctx, cudaSetDevice(ctx->device));
+  uint32_t cap = 2; while (cap < 2u * (uint32_t)n) cap <<= 1;
+  Scratch scratch(ctx);
+  char* table = nullptr;
+  const int Wb = (W + 1) / 2, Hb = (H + 1) / 2, Db = (D + 1) / 2;
+  const size_t table_bytes = (size_t)cap * (sizeof(unsigned long long) + sizeof(BrickVals));
+  T2_CUDA(ctx, scratch.get(&table, table_bytes));
+  unsigned long long* bkeys = (unsigned long long*)table; BrickVals* bvals = (BrickVals*)(table + (size_t)cap * sizeof(unsigned long long));
+  T2_CUDA(ctx, cudaMemsetAsync(table, 0xff, table_bytes, ctx->stream));
+  if (n > 0) {
+    k_brick_insert<<<cdiv_i(n, 256), 256, 0, ctx->stream>>>((const int4*)coords, (int)n, Wb, Hb, Db, bkeys, bvals, cap - 1);
+    T2_LAUNCHED(ctx);
+  }
+  k_brick_lookup<<<cdiv_i(m, 256), 256, 0, ctx->stream>>>((const int4*)queries, m, W, H, D, Wb, Hb, Db, bkeys, bvals, cap - 1, rows);
   T2_LAUNCHED(ctx);
   return T2SC_OK;
 }

@@ -31,11 +31,13 @@ __device__ __forceinline__ uint32_t mask_key(uint32_t g) {
   return b;
 }
 
-// key = group | block (block_bits wide) | mask key (27 bits), most significant first
+// key = group | block (block_bits wide) | mask key (27 bits), most significant first, with the `drop` least significant
+// mask-key bits left out; K is uint32_t when that fits in 32 bits (half the sort traffic), else unsigned long long.
 // halo_from > 0 (split plan, no src): group 1 = rows with a map entry >= halo_from (a row of a peer), group 0 = the rest
+template <class K>
 __global__ void k_plan_keys(const int* __restrict__ gray, const int* __restrict__ src, const uint32_t* __restrict__ nbr, uint32_t halo_from,
-                            i64 m, i64 block_rows, int block_bits,
-                            unsigned long long* __restrict__ keys, int* __restrict__ iota, int* __restrict__ group_cnt) {
+                            i64 m, i64 block_rows, int block_bits, int drop,
+                            K* __restrict__ keys, int* __restrict__ iota, int* __restrict__ group_cnt) {
   i64 i = blockIdx.x * (i64)blockDim.x + threadIdx.x;
   if (i >= m) return;
   int grp = 0; i64 nrow = i;
@@ -46,77 +48,85 @@ __global__ void k_plan_keys(const int* __restrict__ gray, const int* __restrict_
     for (int v = 0; v < 27; v++) { const uint32_t r = __ldg(e + v); grp |= (r != NBR_EMPTY && r >= halo_from) ? 1 : 0; }
   }
   unsigned long long blk = (unsigned long long)(i / block_rows);
-  keys[i] = ((unsigned long long)grp << (27 + block_bits)) | (blk << 27) | mask_key((uint32_t)gray[nrow]);
+  const unsigned long long k = ((unsigned long long)grp << (27 + block_bits)) | (blk << 27) | mask_key((uint32_t)gray[nrow]);
+  keys[i] = (K)(k >> drop);
   iota[i] = (int)i;
   if (src || halo_from) atomicAdd(&group_cnt[grp], 1);
-}
-
-// one thread: tile offsets of the (up to 8) groups
-// bounds[0..2] = {0, first boundary tile, number of tiles}: the interior part of a split plan is tiles
-// [bounds[0], bounds[1]), its boundary part [bounds[1], bounds[2]); any other plan is all interior.
-__global__ void k_plan_groups(const int* __restrict__ group_cnt, int ngroups, int split, i64 m, int TILE, int* __restrict__ gmeta, int* __restrict__ bounds) {
-  // gmeta[g] = first row of group g, gmeta[16+g] = first tile of group g
-  int row = 0, tile = 0;
-  for (int g = 0; g < ngroups; g++) {
-    int c = ngroups == 1 ? (int)m : group_cnt[g];
-    gmeta[g] = row; gmeta[16 + g] = tile;
-    row += c; tile += (c + TILE - 1) / TILE;
-  }
-  gmeta[ngroups] = row; gmeta[16 + ngroups] = tile;
-  bounds[0] = 0; bounds[1] = split ? gmeta[16 + 1] : tile; bounds[2] = tile;
-}
-
-// one warp per tile: extent, weight base, OR of the row masks; also the plan's tap statistics
-__global__ void k_plan_tiles(const int* __restrict__ gray, const int* __restrict__ src, const int* __restrict__ order,
-                             const int* __restrict__ gmeta, int ngroups, int split, int TILE, const int* __restrict__ ntiles,
-                             PlanTile* __restrict__ tiles, unsigned long long* __restrict__ stats) {
-  int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (t >= *ntiles) return;
-  int g = 0;
-  while (g + 1 < ngroups && t >= gmeta[16 + g + 1]) g++;
-  int start = gmeta[g] + (t - gmeta[16 + g]) * TILE;
-  int rows = min(TILE, gmeta[g + 1] - start);
-  uint32_t o = 0; int act = 0;
-  for (int j = lane; j < rows; j += 32) {
-    int r = order[start + j];
-    int nrow = src ? (src[r] >> 3) : r;
-    uint32_t gm = (uint32_t)gray[nrow];
-    o |= gm; act += __popc(gm);
-  }
-  o = __reduce_or_sync(0xffffffffu, o);
-  act = __reduce_add_sync(0xffffffffu, act);
-  if (o == 0) o = 1u << 13;       // no row of the tile has any neighbour: one tap of zero-filled rows still initialises the accumulators
-  if (lane == 0) {
-    tiles[t] = PlanTile{start, rows, split ? 0 : g, o};      // wbase holds the child slot (the conv multiplies by Co); the two parts of a split plan share one weight set
-    atomicAdd(&stats[0], (unsigned long long)rows * __popc(o));
-    atomicAdd(&stats[1], (unsigned long long)act);
-  }
 }
 
 // The neighbour map in tile order: table[t][v][j] = entry of tap v of the j-th row of tile t (for a subdivision plan: of
 // that child's parent), 0x80000000 for an absent neighbour and for j past the tile's rows.  One CTA per tile; the rows
 // are read as they lie in the caller's map (27 consecutive words) and written tap-major through shared memory.
+// HEADER: the same CTA first works out its tile from the group counts (extent, weight group, OR of the row masks), writes
+// the tile descriptor, the plan's tap statistics and (CTA 0) the part bounds {0, first boundary tile, number of tiles}:
+// the interior part of a split plan is tiles [bounds[0], bounds[1]), its boundary part [bounds[1], bounds[2]); any other
+// plan is all interior.  Without HEADER the descriptors are read back (rebuild of the table alone).
 constexpr uint32_t TABLE_ABSENT = 0x80000000u;
-template <int TILE>
-__global__ void __launch_bounds__(256) k_plan_table(const uint32_t* __restrict__ nbr, const int* __restrict__ src, const int* __restrict__ order,
-                                                    const PlanTile* __restrict__ tiles, const int* __restrict__ ntiles, uint32_t* __restrict__ table) {
+template <int TILE, bool HEADER>
+__global__ void __launch_bounds__(256) k_plan_tiles_table(const uint32_t* __restrict__ nbr, const int* __restrict__ gray, const int* __restrict__ src,
+                                                          const int* __restrict__ order, const int* __restrict__ group_cnt, int ngroups, int split,
+                                                          i64 m, PlanTile* __restrict__ tiles, int* __restrict__ bounds,
+                                                          unsigned long long* __restrict__ stats, uint32_t* __restrict__ table,
+                                                          uint32_t* __restrict__ max_entry) {
   const int t = blockIdx.x;
-  if (t >= *ntiles) return;
   __shared__ int s_row[TILE];
   __shared__ uint32_t s_e[27 * (TILE + 1)];
-  const PlanTile tile = tiles[t];
-  for (int j = threadIdx.x; j < TILE; j += 256) {
-    int nr = -1;
-    if (j < tile.rows) { const int r = order[tile.start + j]; nr = src ? (src[r] >> 3) : r; }
-    s_row[j] = nr;
+  __shared__ uint32_t s_or;
+  __shared__ int s_act;
+  PlanTile tile;
+  if constexpr (HEADER) {
+    // first row / first tile of every group; a group's tiles never mix with another's
+    int row = 0, tl = 0, g = 0, start = 0, rows = 0, first_boundary = 0;
+    bool mine = false;
+    for (int q = 0; q < ngroups; q++) {
+      const int c = ngroups == 1 ? (int)m : group_cnt[q];
+      const int nt = (c + TILE - 1) / TILE;
+      if (q == 1) first_boundary = tl;
+      if (!mine && t < tl + nt) { mine = true; g = q; start = row + (t - tl) * TILE; rows = min(TILE, row + c - start); }
+      row += c; tl += nt;
+    }
+    if (t == 0 && threadIdx.x == 0) { bounds[0] = 0; bounds[1] = split ? first_boundary : tl; bounds[2] = tl; }
+    if (!mine) return;
+    if (threadIdx.x == 0) { s_or = 0; s_act = 0; }
+    tile = PlanTile{start, rows, split ? 0 : g, 0};      // wbase holds the child slot (the conv multiplies by Co); the two parts of a split plan share one weight set
+  } else {
+    if (t >= bounds[2]) return;
+    tile = tiles[t];
   }
   __syncthreads();
+  uint32_t o = 0; int act = 0;
+  for (int j = threadIdx.x; j < TILE; j += 256) {
+    int nr = -1;
+    if (j < tile.rows) {
+      const int r = order[tile.start + j]; nr = src ? (src[r] >> 3) : r;
+      if constexpr (HEADER) { const uint32_t gm = (uint32_t)gray[nr]; o |= gm; act += __popc(gm); }
+    }
+    s_row[j] = nr;
+  }
+  if constexpr (HEADER) {
+    o = __reduce_or_sync(0xffffffffu, o); act = __reduce_add_sync(0xffffffffu, act);
+    if ((threadIdx.x & 31) == 0) { atomicOr(&s_or, o); atomicAdd(&s_act, act); }
+  }
+  __syncthreads();
+  if constexpr (HEADER) {
+    if (threadIdx.x == 0) {
+      uint32_t mask = s_or;
+      if (mask == 0) mask = 1u << 13;       // no row of the tile has any neighbour: one tap of zero-filled rows still initialises the accumulators
+      tile.mask = mask;
+      tiles[t] = tile;
+      atomicAdd(&stats[0], (unsigned long long)tile.rows * __popc(mask));
+      atomicAdd(&stats[1], (unsigned long long)s_act);
+    }
+  }
+  uint32_t big = 0;         // the largest present entry: lets the bounds check skip its scan when every entry is in range
   for (int e = threadIdx.x; e < TILE * 27; e += 256) {
     const int j = e / 27, v = e - j * 27, nr = s_row[j];
     uint32_t val = TABLE_ABSENT;
-    if (nr >= 0) { val = __ldg(nbr + (i64)nr * 27 + v); if (val == NBR_EMPTY) val = TABLE_ABSENT; }
+    if (nr >= 0) { val = __ldg(nbr + (i64)nr * 27 + v); if (val == NBR_EMPTY) val = TABLE_ABSENT; else big = max(big, val); }
     s_e[v * (TILE + 1) + j] = val;
   }
+  big = __reduce_max_sync(0xffffffffu, big);
+  if ((threadIdx.x & 31) == 0 && big > *(volatile uint32_t*)max_entry) atomicMax(max_entry, big);
   __syncthreads();
   uint32_t* out = table + (i64)t * 27 * TILE;
   for (int e = threadIdx.x; e < TILE * 27; e += 256) {
@@ -125,8 +135,10 @@ __global__ void __launch_bounds__(256) k_plan_table(const uint32_t* __restrict__
   }
 }
 
-// entries at or above n_in become absent and are reported (status bit 8)
-__global__ void k_plan_table_check(uint32_t* __restrict__ table, const int* __restrict__ ntiles, int per_tile, uint32_t n_in, int* status) {
+// entries at or above n_in (the rows of the feature array) become absent and are reported (status bit 8)
+__global__ void k_plan_table_check(uint32_t* __restrict__ table, const int* __restrict__ ntiles, int per_tile, uint32_t n_in, int* status,
+                                   const uint32_t* __restrict__ max_entry) {
+  if (*max_entry < n_in) return;          // the usual case: nothing to blank, nothing to scan
   const i64 n = (i64)*ntiles * per_tile;
   bool bad = false;
   for (i64 i = blockIdx.x * (i64)blockDim.x + threadIdx.x; i < n; i += (i64)gridDim.x * blockDim.x) {
@@ -136,28 +148,38 @@ __global__ void k_plan_table_check(uint32_t* __restrict__ table, const int* __re
   if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicOr(status, 256);
 }
 
-int plan_table_build(t2sc_ctx* ctx, t2sc_plan* p) {
+template <bool HEADER>
+int plan_tiles_table(t2sc_ctx* ctx, t2sc_plan* p, const int32_t* gray, const int* gcnt, int ngroups) {
   if (p->n_out == 0) return T2SC_OK;
   if (p->tile_rows == 128)
-    k_plan_table<128><<<(unsigned)p->max_tiles, 256, 0, ctx->stream>>>(p->nbr, p->src, p->order, p->tiles, p->ntiles, p->tnbr);
+    k_plan_tiles_table<128, HEADER><<<(unsigned)p->max_tiles, 256, 0, ctx->stream>>>(p->nbr, gray, p->src, p->order, gcnt, ngroups, p->split ? 1 : 0, p->n_out,
+                                                                                       p->tiles, p->bounds, p->stats, p->tnbr, (uint32_t*)(p->meta + 11));
   else
-    k_plan_table<256><<<(unsigned)p->max_tiles, 256, 0, ctx->stream>>>(p->nbr, p->src, p->order, p->tiles, p->ntiles, p->tnbr);
+    k_plan_tiles_table<256, HEADER><<<(unsigned)p->max_tiles, 256, 0, ctx->stream>>>(p->nbr, gray, p->src, p->order, gcnt, ngroups, p->split ? 1 : 0, p->n_out,
+                                                                                       p->tiles, p->bounds, p->stats, p->tnbr, (uint32_t*)(p->meta + 11));
   T2_LAUNCHED(ctx);
   return T2SC_OK;
 }
 
 }  // namespace
 
-// Called by the conv launcher: the table holds no entry at or above n_in.  The check runs once per n_in; when n_in changes
-// after a check the table is rebuilt from the caller's map first, because the earlier check may have blanked entries
-// that are in range now.
+// The table holds no entry at or above n_in: checked once per n_in, by t2sc_plan_check or by the first conv that comes
+// with that n_in.  When n_in changes after a check the table is rebuilt from the caller's map first, because the earlier
+// check may have blanked entries that are in range now.
 int plan_table_prepare(t2sc_ctx* ctx, t2sc_plan* p, i64 n_in) {
   if (p->table_n_in == n_in || p->n_out == 0) return T2SC_OK;
-  if (p->table_n_in >= 0) { int rc = plan_table_build(ctx, p); if (rc != T2SC_OK) return rc; }
-  k_plan_table_check<<<2 * ctx->num_sms, 256, 0, ctx->stream>>>(p->tnbr, p->ntiles, 27 * p->tile_rows, (uint32_t)n_in, ctx->status);
+  if (p->table_n_in >= 0) { int rc = plan_tiles_table<false>(ctx, p, nullptr, nullptr, 0); if (rc != T2SC_OK) return rc; }
+  k_plan_table_check<<<2 * ctx->num_sms, 256, 0, ctx->stream>>>(p->tnbr, p->ntiles, 27 * p->tile_rows, (uint32_t)n_in, ctx->status, (const uint32_t*)(p->meta + 11));
   T2_LAUNCHED(ctx);
   p->table_n_in = n_in;
   return T2SC_OK;
+}
+
+extern "C" int t2sc_plan_check(t2sc_ctx* ctx, t2sc_plan* p, int64_t n_in) {
+  T2_REQ(ctx, ctx && p, "null context or plan");
+  T2_REQ(ctx, n_in >= p->n_rows && n_in < (1ll << 31), "n_in=%lld for a map over %lld rows", (long long)n_in, (long long)p->n_rows);
+  T2_CUDA(ctx, cudaSetDevice(ctx->device));
+  return plan_table_prepare(ctx, p, n_in);
 }
 
 static int plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_t* gray, int64_t n_rows,
@@ -179,9 +201,8 @@ static int plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_t* gray, 
   p->split = split != 0;
   int ngroups = src ? 8 : (split ? 2 : 1);
   p->max_tiles = cdiv_i(m, TILE) + (src ? 8 : (split ? 2 : 0));
-  unsigned long long *keys = nullptr, *keys2 = nullptr; int *iota = nullptr, *gcnt = nullptr, *gmeta = nullptr; void* tmp = nullptr;
+  Scratch scratch(ctx);            // sort buffers: back to the pool on every path out
   auto fail = [&](cudaError_t e) {
-    t2_free(ctx, keys); t2_free(ctx, keys2); t2_free(ctx, iota); t2_free(ctx, gcnt); t2_free(ctx, gmeta); t2_free(ctx, tmp);
     t2sc_plan_destroy(ctx, p);
     return t2sc_fail(ctx, T2SC_ERR_CUDA, "t2sc_plan_create: %s", cudaGetErrorString(e));
   };
@@ -190,35 +211,43 @@ static int plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_t* gray, 
   PL(t2_alloc(ctx, &p->order, (size_t)m));
   PL(t2_alloc(ctx, &p->tiles, (size_t)p->max_tiles));
   PL(t2_alloc(ctx, &p->tnbr, (size_t)p->max_tiles * 27 * tile_rows));
-  PL(t2_alloc(ctx, &p->bounds, 3));
-  p->ntiles = p->bounds + 2;
-  PL(t2_alloc(ctx, &p->stats, 2));
-  PL(cudaMemsetAsync(p->bounds, 0, 3 * sizeof(int), ctx->stream));
-  PL(cudaMemsetAsync(p->stats, 0, 2 * sizeof(unsigned long long), ctx->stream));
+  // one small block, one memset: group counts [0..8), part bounds [8..11), largest map entry [11], tap statistics (two u64) from int 12
+  PL(t2_alloc(ctx, &p->meta, 16));
+  p->bounds = p->meta + 8; p->ntiles = p->bounds + 2; p->stats = (unsigned long long*)(p->meta + 12);
+  PL(cudaMemsetAsync(p->meta, 0, 16 * sizeof(int), ctx->stream));
   if (m > 0) {
-    PL(t2_alloc(ctx, &keys, (size_t)m)); PL(t2_alloc(ctx, &keys2, (size_t)m)); PL(t2_alloc(ctx, &iota, (size_t)m));
-    PL(t2_alloc(ctx, &gcnt, 8)); PL(t2_alloc(ctx, &gmeta, 32));
-    PL(cudaMemsetAsync(gcnt, 0, 8 * sizeof(int), ctx->stream));
     int block_bits = 0;
     while (((m + block_rows - 1) / block_rows) > (1ll << block_bits)) block_bits++;
-    k_plan_keys<<<cdiv_i(m, 256), 256, 0, ctx->stream>>>(gray, src, nbr, (uint32_t)halo_from, m, block_rows, block_bits, keys, iota, gcnt);
-    ctx->launches++; PL(cudaGetLastError());
-    size_t tb = 0;
-    int end_bit = 27 + block_bits + (src ? 3 : (split ? 1 : 0));
     // the 3 least significant key bits (centre tap and two face taps) do not change the tiles' masks measurably
     // (active/computed 0.855 -> 0.853) and leaving them out saves a radix pass on maps sorted as one block
-    const int begin_bit = 3;
-    PL(cub::DeviceRadixSort::SortPairs(nullptr, tb, keys, keys2, iota, p->order, (int)m, begin_bit, end_bit, ctx->stream));
-    PL(t2_alloc(ctx, (char**)&tmp, tb));
-    PL(cub::DeviceRadixSort::SortPairs(tmp, tb, keys, keys2, iota, p->order, (int)m, begin_bit, end_bit, ctx->stream));
-    k_plan_groups<<<1, 1, 0, ctx->stream>>>(gcnt, ngroups, split, m, TILE, gmeta, p->bounds);
-    ctx->launches++; PL(cudaGetLastError());
-    k_plan_tiles<<<cdiv_i(p->max_tiles * 32, 256), 256, 0, ctx->stream>>>(gray, src, p->order, gmeta, ngroups, split, TILE, p->ntiles, p->tiles, p->stats);
-    ctx->launches++; PL(cudaGetLastError());
-    if (plan_table_build(ctx, p) != T2SC_OK) return fail(cudaGetLastError());
+    // Up to five more go when that brings the key down to 32 bits (a large subdivision plan: 3 group bits + 6 block bits).
+    int drop = 3;
+    while (27 + block_bits + (src ? 3 : (split ? 1 : 0)) - drop > 32 && drop < 8) drop++;
+    const int key_bits = 27 + block_bits + (src ? 3 : (split ? 1 : 0)) - drop;
+    const bool narrow = key_bits <= 32;
+    const size_t ksz = narrow ? sizeof(uint32_t) : sizeof(unsigned long long);
+    char* buf = nullptr; char* tmp = nullptr; size_t tb = 0;
+    const size_t koff = ((size_t)m * ksz + 255) & ~(size_t)255;
+    PL(scratch.get(&buf, 2 * koff + (size_t)m * sizeof(int)));
+    int* iota = (int*)(buf + 2 * koff);
+    if (narrow) {
+      uint32_t *keys = (uint32_t*)buf, *keys2 = (uint32_t*)(buf + koff);
+      k_plan_keys<uint32_t><<<cdiv_i(m, 256), 256, 0, ctx->stream>>>(gray, src, nbr, (uint32_t)halo_from, m, block_rows, block_bits, drop, keys, iota, p->meta);
+      ctx->launches++; PL(cudaGetLastError());
+      PL(cub::DeviceRadixSort::SortPairs(nullptr, tb, keys, keys2, iota, p->order, (int)m, 0, key_bits, ctx->stream));
+      PL(scratch.get(&tmp, tb));
+      PL(cub::DeviceRadixSort::SortPairs(tmp, tb, keys, keys2, iota, p->order, (int)m, 0, key_bits, ctx->stream));
+    } else {
+      unsigned long long *keys = (unsigned long long*)buf, *keys2 = (unsigned long long*)(buf + koff);
+      k_plan_keys<unsigned long long><<<cdiv_i(m, 256), 256, 0, ctx->stream>>>(gray, src, nbr, (uint32_t)halo_from, m, block_rows, block_bits, drop, keys, iota, p->meta);
+      ctx->launches++; PL(cudaGetLastError());
+      PL(cub::DeviceRadixSort::SortPairs(nullptr, tb, keys, keys2, iota, p->order, (int)m, 0, key_bits, ctx->stream));
+      PL(scratch.get(&tmp, tb));
+      PL(cub::DeviceRadixSort::SortPairs(tmp, tb, keys, keys2, iota, p->order, (int)m, 0, key_bits, ctx->stream));
+    }
+    if (plan_tiles_table<true>(ctx, p, gray, p->meta, ngroups) != T2SC_OK) return fail(cudaGetLastError());
   }
 #undef PL
-  t2_free(ctx, keys); t2_free(ctx, keys2); t2_free(ctx, iota); t2_free(ctx, gcnt); t2_free(ctx, gmeta); t2_free(ctx, tmp);
   *out = p;
   return T2SC_OK;
 }
@@ -256,7 +285,7 @@ extern "C" int t2sc_plan_destroy(t2sc_ctx* ctx, t2sc_plan* p) {
   if (!p) return T2SC_OK;
   T2_REQ(ctx, ctx != nullptr, "null context");
   cudaSetDevice(ctx->device);
-  t2_free(ctx, p->order); t2_free(ctx, p->tiles); t2_free(ctx, p->tnbr); t2_free(ctx, p->bounds); t2_free(ctx, p->stats);
+  t2_free(ctx, p->order); t2_free(ctx, p->tiles); t2_free(ctx, p->tnbr); t2_free(ctx, p->meta);
   delete p;
   return T2SC_OK;
 }

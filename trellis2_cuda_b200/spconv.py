@@ -120,6 +120,13 @@ class _Plan:
             self.ctx.check(self.ctx.lib.t2sc_plan_set_input_rows(self.ctx.h, self.h, n_in))
             self._n_in = n_in
 
+    def check(self, n_in: int) -> "_Plan":
+        """Runs the one-time bounds check of the plan's map copy against a feature array of n_in rows now instead of in the
+        first conv."""
+        self.set_input_rows(n_in)
+        self.ctx.check(self.ctx.lib.t2sc_plan_check(self.ctx.h, self.h, n_in))
+        return self
+
     def order(self) -> torch.Tensor:
         o = torch.empty(self.n_out, dtype=torch.int32, device=self.nbr.device)
         self.ctx.check(self.ctx.lib.t2sc_plan_order(self.ctx.h, self.h, _ptr(o)))
@@ -213,6 +220,18 @@ def build_neighbors_range(coords: torch.Tensor, row_lo: int, row_hi: int, W: int
     gray = torch.empty(m, dtype=torch.int32, device=coords.device)
     ctx.check(ctx.lib.t2sc_build_neighbors_range(ctx.h, _ptr(coords), coords.shape[0], W, H, D, row_lo, row_hi, _ptr(nbr), _ptr(gray)))
     return nbr, gray
+
+
+def voxel_lookup(coords: torch.Tensor, queries: torch.Tensor, W: int = 4096, H: int = 4096, D: int = 4096) -> torch.Tensor:
+    """rows[q] = index of the row of `coords` [n,4] equal to `queries[q]` = (b,x,y,z), or -1: the lookup of the reference's
+    vhash_find (src/mesh.cu:7-19) over this library's voxel hash."""
+    _chk(coords, "coords", torch.int32, 2); _chk(queries, "queries", torch.int32, 2)
+    if coords.shape[1] != 4 or queries.shape[1] != 4:
+        raise T2scError(-1, "coords and queries must be [*,4]")
+    ctx = context(coords.device)
+    rows = torch.empty(queries.shape[0], dtype=torch.int32, device=coords.device)
+    ctx.check(ctx.lib.t2sc_voxel_lookup(ctx.h, _ptr(coords), coords.shape[0], W, H, D, _ptr(queries), queries.shape[0], _ptr(rows)))
+    return rows
 
 
 def cache_from_map(coords_like: torch.Tensor, nbr: torch.Tensor, gray: torch.Tensor, block_rows: int = 0, tile_rows: int = 0) -> SpConvCache:
@@ -349,9 +368,10 @@ class Level:
     _up_plans: Optional[dict] = None
 
     def up_plan_for(self, Cc: int) -> _Plan:
-        """Schedule of the subdivision conv into Cc child channels: 256-row tiles (two 128-row accumulators per weight
-        slab) for 256-column slabs, 128-row tiles below, where the several-units-per-stage form of the kernel runs."""
-        tr = 256 if Cc % 256 == 0 else 128
+        """Schedule of the subdivision conv into Cc child channels: 256-row tiles, two 128-row accumulators per weight slab
+        (the 8 child slots have 8 weight sets, so a slab is reused by fewer rows than in a submanifold conv; measured on
+        886,752 parents -> 3,288,465 children, 128 -> 64: 2.35 ms against 2.80 ms with 128-row tiles)."""
+        tr = 256
         if self._up_plans is None:
             self._up_plans = {}
         if tr not in self._up_plans:
