@@ -149,7 +149,7 @@ int t2sc_plan_order(t2sc_ctx* ctx, t2sc_plan* plan, int32_t* order_out);
  * rounded (src/ops.cu:17-76) -> activation, rounded (src/ops.cu:79-90) -> + residual, rounded
  * (add_, src/ops.cu:105-113) -> + skip (k_add_skip, src/sdec.cu:39-43). */
 typedef struct {
-  const void* bias;        /* [Co] (subdivision conv: [8*Co]) in the feature dtype, or NULL */
+  const void* bias;        /* [Co] (subdivision conv: [8*Co]) in the feature dtype, or NULL; bias and residual 16-byte aligned */
   int ln;                  /* 0 = none, 1 = LayerNorm over the Co output channels */
   const float* ln_gamma;   /* fp32 [Co] or NULL (no affine) */
   const float* ln_beta;    /* fp32 [Co] or NULL */
@@ -210,6 +210,13 @@ int t2sc_peer_barrier(t2sc_ctx* ctx, void* const* flags_peers, int n_peers, int 
 /* Replaces layer_norm + act_ + add_ (src/ops.cu:17-113) as one pass over [n,C]; any of the three may
  * be disabled (ln = 0, act = 0, residual = NULL).  In place when y == x. */
 int t2sc_row_epilogue(t2sc_ctx* ctx, const void* x, const t2sc_epilogue* ep, void* y, int64_t n, int C, int dtype);
+
+/* Replaces linear (src/gemm.cu:25-64, a cuBLAS call in the reference) for the MLP half of the decoder's ConvNeXt block
+ * (src/sdec.cu:62-65: Linear C -> 4C, SiLU, Linear 4C -> C, add_), with the ops around it fused: y [n,Co] = epilogue(x [n,Ci] .
+ * w [Co,Ci]^T).  It runs on the conv's tcgen05 kernel (one tap whose gather reads the row's own input row) and shares its
+ * epilogue: bias, LayerNorm, activation, residual in t2sc_epilogue's order.  fp16 / bf16, Ci % 64 == 0, Co % 32 == 0. */
+int t2sc_linear(t2sc_ctx* ctx, const void* x, const void* w, const t2sc_epilogue* ep, void* y, int dtype,
+                int64_t n, int Ci, int Co);
 
 /* Whole operator with HOST buffers, as apps/parity.cu:148-167 drives it: copies coords / x / w / bias
  * in, builds the neighbour map, runs the conv, copies y back and synchronises.  bias_host may be NULL. */

@@ -34,19 +34,20 @@ def host(t):
 ULP = {"f16": 2.0 ** -10, "bf16": 2.0 ** -7, "f32": 2.0 ** -23}
 
 
-def check_feats(got, want, what="", dt=None):
+def check_feats(got, want, what="", dt=None, mean_rel=True, ulps=1):
     """max-abs <= 2e-2 and mean-rel <= 2e-3.  With `dt` given (outputs that went through LayerNorm or an
     activation, whose magnitude is not bounded near 1) one rounding step of the storage dtype is also
-    accepted where it exceeds 2e-2: a bf16 value in [4, 8) cannot differ by less than 3.1e-2."""
+    accepted where it exceeds 2e-2: a bf16 value in [4, 8) cannot differ by less than 3.1e-2.  `ulps` = 2 for a chain of
+    two rounded ops over millions of values, where a flipped first rounding and a tie in the second one do meet."""
     got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
     assert got.shape == want.shape, what
     assert np.isfinite(got).all(), what
     err = np.abs(got - want)
     allow = np.full_like(err, MAX_ABS)
     if dt is not None:
-        allow = np.maximum(allow, ULP[dt] * 2.0 ** np.floor(np.log2(np.maximum(np.abs(want), 1e-30))))
+        allow = np.maximum(allow, ulps * ULP[dt] * 2.0 ** np.floor(np.log2(np.maximum(np.abs(want), 1e-30))))
     mr = err.sum() / max(np.abs(want).sum(), 1e-30)
-    assert (err <= allow).all() and mr <= MEAN_REL, f"{what}: max-abs {err.max():.3e} mean-rel {mr:.3e}"
+    assert (err <= allow).all() and (mr <= MEAN_REL or not mean_rel), f"{what}: max-abs {err.max():.3e} mean-rel {mr:.3e}"
 
 
 def random_coords(rng, n, res, batches=1):
@@ -618,6 +619,43 @@ def test_peer_barrier_is_bounded(sp):
     assert f0.tolist()[:2] == [1, 1] and f1.tolist()[:2] == [1, 1]
     with pytest.raises(sp.T2scError, match="timeout_ms"):
         sp.peer_barrier(ctx, ptrs, 0, 2, timeout_ms=0)
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+@pytest.mark.parametrize("n,Ci,Co", [(1, 64, 32), (130, 64, 256), (5000, 128, 512), (5000, 512, 128), (20001, 256, 1024), (20001, 1024, 256), (777, 192, 96)])
+def test_linear_with_fused_tail_matches_fp32(sp, dt, n, Ci, Co):
+    """The MLP half of the reference decoder's ConvNeXt block (Linear C -> 4C, SiLU, Linear 4C -> C, add_) on the conv
+    kernel: against a plain fp32 matmul of the same rounded operands, with the storage rounding after every op where the
+    reference's separate kernels have it (GEMM, bias, activation / LayerNorm, add)."""
+    td = TD[dt]
+    g = torch.Generator(device="cpu").manual_seed(n + Ci + Co)
+    x = (0.5 * torch.randn(n, Ci, generator=g)).to(td).cuda()      # |x.w| stays below 2-3: one rounding step there is under 2e-2
+    w = (torch.randn(Co, Ci, generator=g) / Ci ** 0.5).to(td).cuda()
+    b = (0.1 * torch.randn(Co, generator=g)).to(td).cuda()
+    r = torch.randn(n, Co, generator=g).to(td).cuda()
+    mm = (x.float() @ w.float().t()).to(td)
+    lin = (mm.float() + b.float()).to(td)
+    big = n * Co >= 4096          # over a few dozen values one rounding step of one value is already 2e-3 of the sum
+    check_feats(host(sp.linear(x, w, b)), host(lin), f"linear {Ci}->{Co}", dt, mean_rel=big, ulps=2)
+    check_feats(host(sp.linear(x, w, None)), host(mm), f"linear {Ci}->{Co} without bias", dt, mean_rel=big, ulps=2)
+    silu = torch.nn.functional.silu(lin.float()).to(td)
+    check_feats(host(sp.linear(x, w, b, act="silu")), host(silu), f"linear+silu {Ci}->{Co}", dt, mean_rel=big, ulps=2)
+    res = (lin.float() + r.float()).to(td)
+    out = torch.empty_like(r)
+    assert sp.linear(x, w, b, residual=r, out=out) is out
+    check_feats(host(out), host(res), f"linear+add {Ci}->{Co}", dt, mean_rel=big, ulps=2)
+    gam, bet = (1 + 0.1 * torch.randn(Co, generator=g)).cuda(), (0.1 * torch.randn(Co, generator=g)).cuda()
+    # LayerNorm multiplies a flipped rounding of its input by 1/std (2 here): it is checked on top of the library's own linear output
+    ln = torch.nn.functional.layer_norm(sp.linear(x, w, b).float(), (Co,), gam, bet, 1e-6).to(td)
+    check_feats(host(sp.linear(x, w, b, ln=(gam, bet, 1e-6))), host(ln), f"linear+LN {Ci}->{Co}", dt, mean_rel=big, ulps=2)
+    sp.context().device_status()
+
+
+def test_linear_reports_unsupported_shapes(sp):
+    x, w = torch.zeros(4, 48, dtype=torch.bfloat16, device="cuda"), torch.zeros(64, 48, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(sp.T2scError):
+        sp.linear(x, w)
+    assert sp.linear(torch.zeros(0, 64, dtype=torch.bfloat16, device="cuda"), torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda")).shape == (0, 64)
 
 
 def test_decoder_like_stack_layer_by_layer(sp):

@@ -8,6 +8,6 @@ without one raises.
 from ._lib import T2scError  # noqa: F401
 from .spconv import (  # noqa: F401
     Level, SpConvCache, SpConvCfg, act_, add_, add_skip, build_neighbors, build_neighbors_range, cache_from_map, context,
-    gather_rows, layer_norm, peer_barrier, subm_conv_local, subm_conv_peers, subm_conv_split,
+    gather_rows, layer_norm, linear, peer_barrier, subm_conv_local, subm_conv_peers, subm_conv_split,
     row_epilogue, spconv_cfg, subdiv_conv, subdivide, subm_conv, subm_conv_host, voxel_lookup,
 )

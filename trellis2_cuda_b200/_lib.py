@@ -59,6 +59,7 @@ SYMBOLS = [
     ("t2sc_subm_conv_peers_part", _i32, [_vp, _vp, _vp, ctypes.POINTER(ctypes.c_void_p), _pi64, _i32, _i32, _vp, ctypes.POINTER(Epilogue), _vp, _i32, _i32, _i32, _i32]),
     ("t2sc_peer_barrier", _i32, [_vp, ctypes.POINTER(ctypes.c_void_p), _i32, _i32, _i32, _i32]),
     ("t2sc_subm_conv_peers", _i32, [_vp, _vp, ctypes.POINTER(ctypes.c_void_p), _pi64, _i32, _i32, _vp, ctypes.POINTER(Epilogue), _vp, _i32, _i32, _i32]),
+    ("t2sc_linear", _i32, [_vp, _vp, _vp, ctypes.POINTER(Epilogue), _vp, _i32, _i64, _i32, _i32]),
     ("t2sc_row_epilogue", _i32, [_vp, _vp, ctypes.POINTER(Epilogue), _vp, _i64, _i32, _i32]),
     ("t2sc_subm_conv_host", _i32, [_vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32]),
 ]

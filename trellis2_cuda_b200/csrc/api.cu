@@ -99,6 +99,7 @@ extern "C" int t2sc_subm_conv_part(t2sc_ctx* ctx, t2sc_plan* plan, const void* x
   if (plan->n_out == 0) return T2SC_OK;
   T2_REQ(ctx, x && w && y, "null tensor");
   T2_REQ(ctx, ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((uintptr_t)y % 16 == 0), "x, w, y must be 16-byte aligned");
+  T2_REQ(ctx, !ep || (((uintptr_t)ep->bias % 16 == 0) && ((uintptr_t)ep->residual % 16 == 0)), "epilogue bias and residual must be 16-byte aligned");
   EpiDev e = epi_dev(ep);
   if (e.skip_x) T2_REQ(ctx, e.skip_src && e.skip_cin % 8 == 0 && e.skip_rep > 0 && Co == (e.skip_cin / 8) * e.skip_rep,
                        "skip: Co=%d Cin=%d rep=%d", Co, e.skip_cin, e.skip_rep);
@@ -150,6 +151,28 @@ extern "C" int t2sc_subm_conv_peers_part(t2sc_ctx* ctx, t2sc_plan* plan, const u
     return t2sc_fail(ctx, T2SC_ERR_UNSUPPORTED, "peer conv needs a submanifold plan, fp16/bf16, Ci %% 64 == 0, Co %% 32 == 0, LayerNorm only for Co in {32,64,128,256} (Ci=%d Co=%d dtype=%d)", Ci, Co, dtype);
   return conv_umma_launch(ctx, plan, x_peers[self_rank], w, Co, e, y, dtype, rows_peers[self_rank], Ci, Co, part, x_peers, rows_peers, n_peers,
                           self_rank, peer_nbr);
+}
+
+// ------------------------------------------------------------------------------------------ dense linear layer on the conv kernel
+extern "C" int t2sc_linear(t2sc_ctx* ctx, const void* x, const void* w, const t2sc_epilogue* ep, void* y, int dtype,
+                           int64_t n, int Ci, int Co) {
+  T2_REQ(ctx, ctx != nullptr, "null context");
+  T2_REQ(ctx, n >= 0 && n < (1ll << 31) - 256, "n=%lld", (long long)n);
+  T2_REQ(ctx, Ci > 0 && Co > 0, "linear shapes Ci=%d Co=%d", Ci, Co);
+  if (n == 0) return T2SC_OK;
+  T2_REQ(ctx, x && w && y, "null tensor");
+  T2_REQ(ctx, ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((uintptr_t)y % 16 == 0), "x, w, y must be 16-byte aligned");
+  T2_REQ(ctx, !ep || (((uintptr_t)ep->bias % 16 == 0) && ((uintptr_t)ep->residual % 16 == 0)), "epilogue bias and residual must be 16-byte aligned");
+  EpiDev e = epi_dev(ep);
+  if (!conv_umma_supported(dtype, Ci, Co, e) || e.skip_x)
+    return t2sc_fail(ctx, T2SC_ERR_UNSUPPORTED, "t2sc_linear runs on the tcgen05 path only: fp16/bf16, Ci %% 64 == 0, Co %% 32 == 0, no skip (Ci=%d Co=%d dtype=%d)", Ci, Co, dtype);
+  if (!e.ln || conv_umma_fuses_ln(Co)) return linear_umma_launch(ctx, x, w, e, y, dtype, n, Ci, Co);
+  EpiDev first = e, rest = e;       // LayerNorm over a row wider than one accumulator: GEMM + bias now, the rest in the row pass
+  first.ln = 0; first.act = 0; first.residual = nullptr; first.gamma = first.beta = nullptr;
+  rest.bias = nullptr;
+  int rc = linear_umma_launch(ctx, x, w, first, y, dtype, n, Ci, Co);
+  if (rc != T2SC_OK) return rc;
+  return row_epilogue_launch(ctx, y, rest, y, n, Co, dtype);
 }
 
 // ------------------------------------------------------------------------------------------ barrier over peer-mapped flags

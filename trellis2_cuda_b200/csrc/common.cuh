@@ -156,6 +156,7 @@ bool conv_umma_fuses_ln(int Co);      // can the tcgen05 path hold a whole outpu
 int conv_umma_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const void* w, i64 w_rows, const EpiDev& ep, void* y,
                      int dtype, i64 n_in, int Ci, int Co, int part = T2SC_PART_ALL, const void* const* x_peers = nullptr,
                      const int64_t* rows_peers = nullptr, int n_peers = 0, int self_rank = 0, const uint32_t* peer_nbr = nullptr);
+int linear_umma_launch(t2sc_ctx* ctx, const void* x, const void* w, const EpiDev& ep, void* y, int dtype, i64 n, int Ci, int Co);
 bool conv_umma2_supported(const t2sc_plan* plan, int dtype, int Ci, int Co, const EpiDev& ep);
 int conv_umma2_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const void* w, i64 w_rows, const EpiDev& ep, void* y,
                       int dtype, i64 n_in, int Ci, int Co, int part = T2SC_PART_ALL);

@@ -102,8 +102,14 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int tile0 = *a.tile_lo, ntiles = *a.tile_hi - tile0;
+  // dense_rows > 0 (t2sc_linear): there is no plan; tile t is rows [t * ROWS, t * ROWS + ROWS) with one tap
+  const bool dense = a.dense_rows > 0;
+  const int tile0 = dense ? 0 : *a.tile_lo, ntiles = dense ? (a.dense_rows + ROWS - 1) / ROWS : *a.tile_hi - tile0;
   const PlanTile* const tiles = a.tiles + tile0;
+  auto tile_at = [&](int t) {
+    if (dense) return PlanTile{t * ROWS, min(ROWS, a.dense_rows - t * ROWS), 0, 1u};
+    return tiles[t];
+  };
   const int nitems = ntiles * a.n_cot;
 
   if (warp < 4 || (G == 2 && warp >= warp_group2(MH))) {
@@ -115,15 +121,15 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
     uint32_t it = 0, tt = 0;
     bool alive = true;
     const bool prof = diag(a, 8); long long w_idx = 0, w_empty = 0, t_role = clock64();
-    PlanTile tile_next = blockIdx.x < nitems ? tiles[blockIdx.x / a.n_cot] : PlanTile{};
+    PlanTile tile_next = blockIdx.x < nitems ? tile_at(blockIdx.x / a.n_cot) : PlanTile{};
     for (int item = blockIdx.x; item < nitems; item += gridDim.x, tt++) {
       const PlanTile tile = tile_next;
-      if (item + (int)gridDim.x < nitems) tile_next = tiles[(item + gridDim.x) / a.n_cot];     // in flight while this tile is gathered
+      if (item + (int)gridDim.x < nitems) tile_next = tile_at((item + gridDim.x) / a.n_cot);     // in flight while this tile is gathered
       const uint32_t buf = tt % NTAB;
       // Every gather warp waits for every tile's table, also one that has none of the tile's units (G == 2): a warp can
       // then never release a buffer twice within one phase of its barrier.
       if (threadIdx.x == 0) trace(a, 0, 0, tt);
-      alive &= mbar_wait_t(bar_tready + 8 * buf, (tt / NTAB) & 1, abort_flag, a.status, 32, prof, w_idx);
+      if (!dense) alive &= mbar_wait_t(bar_tready + 8 * buf, (tt / NTAB) & 1, abort_flag, a.status, 32, prof, w_idx);
       if (threadIdx.x == 0) trace(a, 0, 1, tt);
       const uint32_t* tab = itab + buf * TABW + jbase;
       const int nunits = __popc(tile.mask) * nchunk;
@@ -152,8 +158,13 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
             // Table entries: row number (PEERS: (owner << PEER_SHIFT) | row), or RING_ABSENT.  Everything that does not
             // depend on the channel chunk is done here, once per tap, so that a copy costs two instructions (address,
             // cp.async): the gather warps run these in order.
+            if (dense) {
 #pragma unroll
-            for (int i = 0; i < 8 * MH; i++) idx[i] = tab[v * PITCH + 16 * i];
+              for (int i = 0; i < 8 * MH; i++) idx[i] = jbase + 16 * i < tile.rows ? (uint32_t)(tile.start + jbase + 16 * i) : RING_ABSENT;
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8 * MH; i++) idx[i] = tab[v * PITCH + 16 * i];
+            }
             // PEERS: almost every tap reads local rows only (the index warps say so per tap) and takes the plain path with
             // the owner bits masked off.  For a tap with rows of a peer the addresses are formed here: a table load between
             // the copies below would be ordered after each of them and serialise the loop.
@@ -191,7 +202,7 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
       }
       // the tile's last indices are in registers: the index warps may refill this table
       __syncwarp();
-      if (lane == 0 && alive) mbar_arrive(bar_tfree + 8 * buf);
+      if (lane == 0 && alive && !dense) mbar_arrive(bar_tfree + 8 * buf);
       if (threadIdx.x == 0) trace(a, 0, 2, tt);
     }
     cp_async_wait_all();
@@ -202,11 +213,11 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
     if (lane == 0) {
       uint32_t it = 0;
       bool alive = true;        // false once a wait was given up: nothing more is loaded or signalled
-      PlanTile tile_next = blockIdx.x < nitems ? tiles[blockIdx.x / a.n_cot] : PlanTile{};
+      PlanTile tile_next = blockIdx.x < nitems ? tile_at(blockIdx.x / a.n_cot) : PlanTile{};
       for (int item = blockIdx.x; item < nitems && alive; item += gridDim.x) {
         const int tile_id = item / a.n_cot, cot = item - tile_id * a.n_cot;
         const PlanTile tile = tile_next;
-        if (item + (int)gridDim.x < nitems) tile_next = tiles[(item + gridDim.x) / a.n_cot];
+        if (item + (int)gridDim.x < nitems) tile_next = tile_at((item + gridDim.x) / a.n_cot);
         const int wrow = tile.wbase * a.Co + cot * BN;
         const int nunits = __popc(tile.mask) * nchunk;
         uint32_t mk = tile.mask;
@@ -236,7 +247,7 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
     __syncwarp();
   } else if (!PEERS && (warp == WARP_IDX || warp == warp_idx2(MH))) {
     // ===================================================================== neighbour-index table: one bulk copy per tile
-    if (warp == WARP_IDX && lane == 0) {
+    if (warp == WARP_IDX && lane == 0 && !dense) {
       uint32_t tt = 0;
       for (int item = blockIdx.x; item < nitems; item += gridDim.x, tt++) {
         const uint32_t buf = tt % NTAB;
@@ -268,7 +279,7 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
         if (j < tl.rows) { const int r = a.order[tl.start + j]; nr[i] = a.src ? (a.src[r] >> 3) : r; }
       }
     };
-    auto desc_of = [&](int item) { return item < nitems ? tiles[item / a.n_cot] : PlanTile{}; };
+    auto desc_of = [&](int item) { return item < nitems ? tile_at(item / a.n_cot) : PlanTile{}; };
     int nr[NR], nr_next[NR];
     PlanTile tile_n0 = desc_of(blockIdx.x), tile_n1 = desc_of(blockIdx.x + gridDim.x);
     rows_of(tile_n0, nr);
@@ -336,10 +347,10 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
       uint32_t it = 0, acc_it = 0;
       bool alive = true;        // false once a wait was given up: no more MMAs or commits
       const bool prof = diag(a, 8); long long w_full = 0, w_acc = 0, w_issue = 0, w_commit = 0, t_role = clock64();
-      PlanTile tile_next = blockIdx.x < nitems ? tiles[blockIdx.x / a.n_cot] : PlanTile{};
+      PlanTile tile_next = blockIdx.x < nitems ? tile_at(blockIdx.x / a.n_cot) : PlanTile{};
       for (int item = blockIdx.x; item < nitems && alive; item += gridDim.x, acc_it++) {
         const PlanTile tile = tile_next;
-        if (item + (int)gridDim.x < nitems) tile_next = tiles[(item + gridDim.x) / a.n_cot];
+        if (item + (int)gridDim.x < nitems) tile_next = tile_at((item + gridDim.x) / a.n_cot);
         const uint32_t buf = acc_it % NB, aph = (acc_it / NB) & 1;
         trace(a, 3, 0, acc_it);
         alive &= mbar_wait_t(bar_acce + 8 * buf, aph ^ 1, abort_flag, a.status, 4, prof, w_acc);
@@ -391,13 +402,13 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
     const int q = warp & 3, half = (warp - WARP_EPI0) >> 2, j = half * TILE_M + q * 32 + lane;
     uint32_t acc_it = 0;
     const bool prof = diag(a, 8); long long w_accf = 0, t_role = clock64();
-    PlanTile tile_next = blockIdx.x < nitems ? tiles[blockIdx.x / a.n_cot] : PlanTile{};
+    PlanTile tile_next = blockIdx.x < nitems ? tile_at(blockIdx.x / a.n_cot) : PlanTile{};
     for (int item = blockIdx.x; item < nitems; item += gridDim.x, acc_it++) {
       const int tile_id = item / a.n_cot, cot = item - tile_id * a.n_cot;
       const PlanTile tile = tile_next;
-      if (item + (int)gridDim.x < nitems) tile_next = tiles[(item + gridDim.x) / a.n_cot];
+      if (item + (int)gridDim.x < nitems) tile_next = tile_at((item + gridDim.x) / a.n_cot);
       const uint32_t buf = acc_it % NB, aph = (acc_it / NB) & 1;
-      const int orow = j < tile.rows ? a.order[tile.start + j] : -1;
+      const int orow = j < tile.rows ? (dense ? tile.start + j : a.order[tile.start + j]) : -1;
       const int wcol0 = tile.wbase * a.Co + cot * BN;      // bias index of this item's first column
       int sp = 0, ss = 0;
       if (has_skip && orow >= 0) { int sv = a.ep.skip_src[orow]; sp = sv >> 3; ss = sv & 7; }
@@ -556,4 +567,35 @@ int conv_umma_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const 
   }
 #endif
   return rc;
+}
+
+// y [n,Co] = x [n,Ci] . w [Co,Ci]^T through the same kernel: no neighbour map, one "tap" whose gather reads the output
+// row's own input row, weights as a [Co,1,Ci] tensor.  The fused epilogue is the conv's.
+int linear_umma_launch(t2sc_ctx* ctx, const void* x, const void* w, const EpiDev& ep, void* y, int dtype, i64 n, int Ci, int Co) {
+  T2_CUDA(ctx, cudaSetDevice(ctx->device));
+  const int BN = pick_bn(Co);
+  T2_REQ(ctx, BN > 0, "Co=%d", Co);
+  T2_REQ(ctx, !ep.ln || Co == BN, "fused LayerNorm needs the whole row in one tile (Co=%d)", Co);
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return t2sc_fail(ctx, T2SC_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  CUtensorMap tm;
+  cuuint64_t dims[3] = {(cuuint64_t)Ci, 1, (cuuint64_t)Co};
+  cuuint64_t strides[2] = {(cuuint64_t)Ci * 2, (cuuint64_t)Ci * 2};
+  cuuint32_t box[3] = {(cuuint32_t)KCH, 1, (cuuint32_t)BN};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult cr = enc(&tm, dtype == T2SC_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(w),
+                    dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (cr != CUDA_SUCCESS) return t2sc_fail(ctx, T2SC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for weights [%d,%d]", (int)cr, Co, Ci);
+  ConvArgs args;
+  diag_args(args);
+  args.dense_rows = (int)n; args.n_in = (uint32_t)n;
+  args.npeers = 0; args.self_rank = 0;
+  for (int r = 0; r < 8; r++) { args.xp[r] = nullptr; args.xp_rows[r] = 0; }
+  args.tnbr = nullptr; args.nbr = nullptr; args.order = nullptr; args.src = nullptr; args.tiles = nullptr;
+  args.tile_lo = nullptr; args.tile_hi = nullptr; args.status = ctx->status;
+  args.x = x; args.y = y;
+  args.Ci = Ci; args.Co = Co; args.n_cot = Co / BN; args.is_bf16 = dtype == T2SC_BF16; args.ep = ep;
+  const i64 max_items = (i64)cdiv_i(n, TILE_M) * args.n_cot;
+  return dtype == T2SC_BF16 ? launch_t<1, __nv_bfloat16>(ctx, BN, tm, args, max_items) : launch_t<1, __half>(ctx, BN, tm, args, max_items);
 }

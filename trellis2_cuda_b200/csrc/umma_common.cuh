@@ -60,6 +60,8 @@ struct ConvArgs {
   const void* xp[8];
   uint32_t n_in;            // rows of x (PEERS: unused, see xp_rows); a map entry at or above it is reported and read as absent
   uint32_t xp_rows[8];      // PEERS: rows of every peer's array
+  int dense_rows;           // > 0: no neighbour map at all - a plain row-major GEMM over this many rows (t2sc_linear): tile t is rows
+                            // [t * tile rows, ...), its one "tap" reads input row = output row, weights are [Co, 1, Ci]
   long long* trace;         // diagnostic build only (T2SC_TRACE=file): per-tile timestamps of CTA 0's roles, [role][event][tile < 64]
   int wait_limit;           // bounded waits give up after this many cycles >> WAIT_LIMIT_SHIFT
   int dbg_skip;             // diagnostic build only (T2SC_DEBUG_SKIP), always 0 in the shipped library: 1 = no A gather, 2 = no B load,
@@ -79,6 +81,7 @@ __device__ __forceinline__ void trace(const ConvArgs& a, int role, int ev, uint3
 static inline void diag_args(ConvArgs& args) {
   args.dbg_skip = 0;
   args.trace = nullptr;
+  args.dense_rows = 0;
   args.wait_limit = (int)(WAIT_LIMIT_CYCLES >> WAIT_LIMIT_SHIFT);
 #ifdef T2SC_DIAG
   static const int dbg_skip = [] { const char* e = getenv("T2SC_DEBUG_SKIP"); return e ? atoi(e) : 0; }();
@@ -234,46 +237,71 @@ template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v)
 // Fused epilogue of one output row (this thread's TMEM lane) over the BN accumulator columns at `taddr`:
 // round -> + bias -> LayerNorm -> activation -> + residual -> + skip, each rounded to the storage type, then store.
 // All lanes of the warp must call it (tcgen05.ld is warp-collective); orow < 0 loads but does not store.
+// 32 consecutive bias values (16-byte aligned: wcol0 is a multiple of 32) added with the storage rounding
+template <class T>
+__device__ __forceinline__ void add_bias32(float* h, const T* bias) {
+  const uint4* bp = (const uint4*)bias;
+#pragma unroll
+  for (int g = 0; g < 4; g++) {
+    const uint4 bv = __ldg(bp + g); const uint32_t* w32 = (const uint32_t*)&bv;
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      const float2 f = unpack2<T>(w32[e]);
+      h[g * 8 + e * 2] = rnd<T>(h[g * 8 + e * 2] + f.x); h[g * 8 + e * 2 + 1] = rnd<T>(h[g * 8 + e * 2 + 1] + f.y);
+    }
+  }
+}
+
 template <int BN, class T>
 __device__ __forceinline__ void epilogue_row(const ConvArgs& a, uint32_t taddr, int orow, int cot, int wcol0, int sp, int ss) {
   T* y = (T*)a.y;
   const T* bias = (const T*)a.ep.bias; const T* res = (const T*)a.ep.residual; const T* skx = (const T*)a.ep.skip_x;
   float mean = 0.f, rstd = 1.f;
-  if (a.ep.ln) {      // whole row lives in this accumulator (n_cot == 1): two statistics passes over TMEM
-    float sum = 0.f;
+  if (a.ep.ln) {      // whole row lives in this accumulator (n_cot == 1)
+    // ONE statistics pass over TMEM (every tcgen05.ld round trip counts: at Co <= 128 the epilogue is as long as the tile's
+    // MMAs): sums of (h - K) and (h - K)^2 with K = the row's first value, so that mean = K + S1/n and var = S2/n - (S1/n)^2
+    // lose nothing to cancellation that matters beside the storage rounding of the result.
+    float s1 = 0.f, s2 = 0.f, K = 0.f;
     for (int cc = 0; cc < BN / 32; cc++) {
       uint32_t r[32]; tc_ld32(taddr + cc * 32, r); tc_wait_ld();
+      float h[32];
 #pragma unroll
-      for (int i = 0; i < 32; i++) {
-        float h = rnd<T>(__uint_as_float(r[i]));
-        if (bias) h = rnd<T>(h + to_f<T>(bias[wcol0 + cc * 32 + i]));
-        sum += h;
-      }
-    }
-    mean = sum / (float)BN;
-    float qs = 0.f;
-    for (int cc = 0; cc < BN / 32; cc++) {
-      uint32_t r[32]; tc_ld32(taddr + cc * 32, r); tc_wait_ld();
+      for (int i = 0; i < 32; i++) h[i] = rnd<T>(__uint_as_float(r[i]));
+      if (bias) add_bias32<T>(h, bias + wcol0 + cc * 32);
+      if (cc == 0) K = h[0];
 #pragma unroll
-      for (int i = 0; i < 32; i++) {
-        float h = rnd<T>(__uint_as_float(r[i]));
-        if (bias) h = rnd<T>(h + to_f<T>(bias[wcol0 + cc * 32 + i]));
-        float d = h - mean; qs += d * d;
-      }
+      for (int i = 0; i < 32; i++) { const float d = h[i] - K; s1 += d; s2 = fmaf(d, d, s2); }
     }
-    rstd = rsqrtf(qs / (float)BN + a.ep.eps);
+    const float m1 = s1 / (float)BN;
+    mean = K + m1;
+    rstd = rsqrtf(fmaxf(s2 / (float)BN - m1 * m1, 0.f) + a.ep.eps);
+  }
+  // The residual row is read one 32-column block ahead: a block's four 16-byte loads are in flight while the block
+  // before it is converted and stored, instead of a load latency per block.
+  const uint4* rp = res && orow >= 0 ? (const uint4*)(res + (i64)orow * a.Co + cot * BN) : nullptr;
+  uint4 rnext[4];
+  if (rp) {
+#pragma unroll
+    for (int g = 0; g < 4; g++) rnext[g] = __ldg(rp + g);
   }
   for (int cc = 0; cc < BN / 32; cc++) {
-    uint32_t r[32]; tc_ld32(taddr + cc * 32, r); tc_wait_ld();
+    uint32_t r[32]; tc_ld32(taddr + cc * 32, r);
+    uint4 rcur[4];
+    if (rp) {
+#pragma unroll
+      for (int g = 0; g < 4; g++) rcur[g] = rnext[g];
+      if (cc + 1 < BN / 32) {
+#pragma unroll
+        for (int g = 0; g < 4; g++) rnext[g] = __ldg(rp + (cc + 1) * 4 + g);
+      }
+    }
+    tc_wait_ld();
     if (orow < 0) continue;
     const int col = cot * BN + cc * 32;
     float h[32];
 #pragma unroll
-    for (int i = 0; i < 32; i++) {
-      float v = rnd<T>(__uint_as_float(r[i]));
-      if (bias) v = rnd<T>(v + to_f<T>(bias[wcol0 + cc * 32 + i]));
-      h[i] = v;
-    }
+    for (int i = 0; i < 32; i++) h[i] = rnd<T>(__uint_as_float(r[i]));
+    if (bias) add_bias32<T>(h, bias + wcol0 + cc * 32);
     if (a.ep.ln) {
 #pragma unroll
       for (int i = 0; i < 32; i++) {
@@ -283,15 +311,17 @@ __device__ __forceinline__ void epilogue_row(const ConvArgs& a, uint32_t taddr, 
         h[i] = rnd<T>(v);
       }
     }
-    if (a.ep.act) {
+    if (a.ep.act == T2SC_ACT_SILU) {          // one branch per block, not per element
+#pragma unroll
+      for (int i = 0; i < 32; i++) h[i] = rnd<T>(__fdividef(h[i], 1.f + __expf(-h[i])));
+    } else if (a.ep.act) {
 #pragma unroll
       for (int i = 0; i < 32; i++) h[i] = rnd<T>(act_apply(h[i], a.ep.act));
     }
-    if (res) {
-      const uint4* rp = (const uint4*)(res + (i64)orow * a.Co + col);
+    if (rp) {
 #pragma unroll
       for (int g = 0; g < 4; g++) {
-        uint4 rv = __ldg(rp + g); const uint32_t* w32 = (const uint32_t*)&rv;
+        const uint32_t* w32 = (const uint32_t*)&rcur[g];
 #pragma unroll
         for (int e = 0; e < 4; e++) {
           float2 f = unpack2<T>(w32[e]);

@@ -52,6 +52,8 @@ def measure(args, rank, world, local_rank, peaks, ClockSampler, visible_gpu_inde
         coords = torch.empty((N, 4), dtype=torch.int32, device=dev)
     if world > 1:
         dist.broadcast(coords, 0)          # also the first collective: communicator set-up lands here, not in setup_ms
+        warm = torch.zeros(world, dtype=torch.int64, device=dev)
+        dist.all_to_all_single(torch.empty_like(warm), warm)       # ... and the peer-to-peer connections of the first all-to-all
     sync()
     scene_ms = (time.perf_counter() - t_scene) * 1e3
     ctx = sp.context(dev)
@@ -70,6 +72,8 @@ def measure(args, rank, world, local_rank, peaks, ClockSampler, visible_gpu_inde
     nbr_local = plan.nbr_local.contiguous()
     cache = sp.cache_from_map(coords[lo:hi], nbr_local, gray)
     split = cache.split_plan_for(C, C, plan.n_own) if world > 1 else None
+    if split is not None:
+        split.check(plan.n_local)        # the plan's map copy is checked against owned + halo rows now: both parts find it ready, whichever stream runs first
     peer_nbr = sharding.peer_map(nbr_g, starts).contiguous() if p2p else None
     del nbr_g
     st = (split or cache.plan_for(C, C)).stats()
@@ -101,6 +105,13 @@ def measure(args, rank, world, local_rank, peaks, ClockSampler, visible_gpu_inde
     ws = [torch.from_numpy(scenes.kaiming_uniform_weight(C, C, 100 + l)).to(dev).to(td) for l in range(layers)]
     send_buf = torch.empty((max(int(plan.send_idx.numel()), 1), C), dtype=td, device=dev)
     epoch = [0]
+    # The boundary tiles run on a side stream that waits for the halo only: they write rows the interior tiles do not
+    # touch, so they start on the first SMs the interior kernel leaves instead of behind its last tile.
+    main = torch.cuda.current_stream(dev)
+    side = torch.cuda.Stream(dev)
+    with torch.cuda.stream(side):
+        ctx_side = sp.context(dev)
+    halo_ready = torch.cuda.Event()
 
     def step(timers=None):
         a, b = xa, xb
@@ -116,17 +127,25 @@ def measure(args, rank, world, local_rank, peaks, ClockSampler, visible_gpu_inde
                 sp.peer_barrier(ctx, flag_ptrs, rank, epoch[0])
                 if timers:
                     timers[1][l].record()
+                halo_ready.record(main)
                 sp.subm_conv_split(a, ws[l], None, cache, split, "interior", out=b[:plan.n_own], n_local=plan.n_local)
-                sp.subm_conv_peers(ptrs[a.data_ptr()], rows_of, rank, td, C, ws[l], None, cache, out=b[:plan.n_own],
-                                   plan=split, part="boundary", peer_nbr=peer_nbr)
+                with torch.cuda.stream(side):
+                    side.wait_event(halo_ready)
+                    sp.subm_conv_peers(ptrs[a.data_ptr()], rows_of, rank, td, C, ws[l], None, cache, out=b[:plan.n_own],
+                                       plan=split, part="boundary", peer_nbr=peer_nbr, ctx=ctx_side)
+                main.wait_stream(side)
             else:
                 work = sharding.exchange_halo_async(plan, a, lambda xo, idx: sp.gather_rows(xo, idx, C, out=send_buf))
                 if timers:
                     timers[1][l].record()
                 sp.subm_conv_split(a, ws[l], None, cache, split, "interior", out=b[:plan.n_own])     # while the halo rows travel
-                if work is not None:
-                    work.wait()
-                sp.subm_conv_split(a, ws[l], None, cache, split, "boundary", out=b[:plan.n_own])
+                with torch.cuda.stream(side):
+                    if work is not None:
+                        work.wait()                     # the side stream waits for the all-to-all, not the host
+                    else:
+                        side.wait_stream(main)
+                    sp.subm_conv_split(a, ws[l], None, cache, split, "boundary", out=b[:plan.n_own], ctx=ctx_side)
+                main.wait_stream(side)
             a, b = b, a
         if p2p:
             epoch[0] += 1
@@ -135,6 +154,7 @@ def measure(args, rank, world, local_rank, peaks, ClockSampler, visible_gpu_inde
 
     out = step()
     ctx.device_status()
+    ctx_side.device_status()
     for _ in range(max(warmup - 1, 0)):
         step()
     sync()
@@ -147,7 +167,7 @@ def measure(args, rank, world, local_rank, peaks, ClockSampler, visible_gpu_inde
     sync()
     ev = lambda: torch.cuda.Event(enable_timing=True)
     t_reg0 = time.perf_counter()
-    l0 = ctx.launch_count()
+    l0, l0_side = ctx.launch_count(), ctx_side.launch_count()
     step_ms, exch_ms = [], []
     for _ in range(steps):
         tm = ([ev() for _ in range(layers)], [ev() for _ in range(layers)])
@@ -158,9 +178,10 @@ def measure(args, rank, world, local_rank, peaks, ClockSampler, visible_gpu_inde
         sync()
         step_ms.append(s.elapsed_time(e))
         exch_ms.append(sum(tm[0][l].elapsed_time(tm[1][l]) for l in range(layers)) if world > 1 else 0.0)
-    launches = ctx.launch_count() - l0
+    launches = ctx.launch_count() - l0 + ctx_side.launch_count() - l0_side
     t_reg1 = time.perf_counter()
     ctx.device_status()
+    ctx_side.device_status()
 
     e2e = []
     if with_e2e:
@@ -204,7 +225,7 @@ def measure(args, rank, world, local_rank, peaks, ClockSampler, visible_gpu_inde
             full = sp.build_neighbors(coords, want_sorted=False)
             xa1, xb1 = x_full.clone(), torch.empty_like(x_full)
             ms1 = []
-            for i in range(max(single_gpu_steps, 1) + 1):
+            for i in range(max(single_gpu_steps, 3) + 2):
                 s, e = ev(), ev()
                 s.record()
                 a, b = xa1, xb1
@@ -214,7 +235,7 @@ def measure(args, rank, world, local_rank, peaks, ClockSampler, visible_gpu_inde
                     a, b = b, a
                 e.record()
                 sync()
-                if i >= 1:
+                if i >= 2:
                     ms1.append(s.elapsed_time(e))
             single = sum(ms1) / len(ms1)
             ctx.device_status()

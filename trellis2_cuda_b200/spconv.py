@@ -250,13 +250,14 @@ def subm_conv_local(x: torch.Tensor, w: torch.Tensor, b, c: SpConvCache, **kw) -
 
 
 def subm_conv_split(x: torch.Tensor, w: torch.Tensor, b, c: SpConvCache, plan: _Plan, part: str, *, ln=None, act=None,
-                    residual=None, out=None, n_local: Optional[int] = None) -> torch.Tensor:
+                    residual=None, out=None, n_local: Optional[int] = None, ctx: Optional[Context] = None) -> torch.Tensor:
     """One part ("interior" | "boundary" | "all") of a conv over a split plan (:meth:`SpConvCache.split_plan_for`): x has
     the owned rows first and the halo rows appended; the interior part reads owned rows only, so it can run while the
     halo rows are still in flight.  Both parts write into the same `out` [c.N, Co]; the rows of the other part are left
     untouched.  `n_local` (owned + halo rows, the index space of the plan's map) may be given when x itself holds fewer rows
     - the interior part of a rank whose halo rows are never copied because its boundary tiles gather them from peer
-    memory."""
+    memory.  `ctx` runs the part on another context of the same device (another stream): the two parts write disjoint
+    rows, so the boundary part may run on a side stream that waits for the halo only, beside the interior part's tail."""
     if x.shape[0] < c.N:
         raise T2scError(-1, f"spconv shapes: x has {x.shape[0]} rows, cache has {c.N}")
     if n_local is not None and part != "interior":
@@ -269,14 +270,16 @@ def subm_conv_split(x: torch.Tensor, w: torch.Tensor, b, c: SpConvCache, plan: _
     plan.set_input_rows(n_in)
     y = out if out is not None else torch.empty((plan.n_out, Co), dtype=x.dtype, device=x.device)
     e, keep = _epilogue(Co, x.dtype, b, ln, act, residual, None)
-    plan.keep = keep
-    c.ctx.check(c.ctx.lib.t2sc_subm_conv_part(c.ctx.h, plan.h, _ptr(x), _ptr(w), ctypes.byref(e), _ptr(y), _DT[x.dtype], n_in, Ci, Co,
-                                              0, _lib.PART[part]))
+    ctx = ctx or c.ctx
+    setattr(plan, "keep_" + part, keep)
+    ctx.check(ctx.lib.t2sc_subm_conv_part(ctx.h, plan.h, _ptr(x), _ptr(w), ctypes.byref(e), _ptr(y), _DT[x.dtype], n_in, Ci, Co,
+                                          0, _lib.PART[part]))
     return y
 
 
 def subm_conv_peers(x_ptrs, x_rows, rank: int, x_dtype, Ci: int, w: torch.Tensor, b, c: SpConvCache, *, ln=None, act=None, residual=None,
-                    out=None, plan: Optional[_Plan] = None, part: str = "all", peer_nbr: Optional[torch.Tensor] = None):
+                    out=None, plan: Optional[_Plan] = None, part: str = "all", peer_nbr: Optional[torch.Tensor] = None,
+                    ctx: Optional[Context] = None):
     """subm_conv for one rank of a Morton-range partition whose neighbour map holds (owner << 28) | row entries:
     the rows are gathered straight from the peers' feature arrays (`x_ptrs[r]` = device address of rank r's array
     mapped into this process, `x_rows[r]` its row count, `x_ptrs[rank]` the local one), so no halo is packed or
@@ -288,10 +291,11 @@ def subm_conv_peers(x_ptrs, x_rows, rank: int, x_dtype, Ci: int, w: torch.Tensor
     plan = plan or c.plan_for(Co, Ci)
     y = out if out is not None else torch.empty((plan.n_out, Co), dtype=x_dtype, device=w.device)
     e, keep = _epilogue(Co, x_dtype, b, ln, act, residual, None)
-    plan.keep = keep + ([peer_nbr] if peer_nbr is not None else [])
+    plan.keep_peers = keep + ([peer_nbr] if peer_nbr is not None else [])
     arr = (ctypes.c_void_p * len(x_ptrs))(*[int(p) for p in x_ptrs])
     rows = (ctypes.c_int64 * len(x_ptrs))(*[int(r) for r in x_rows])
-    c.ctx.check(c.ctx.lib.t2sc_subm_conv_peers_part(c.ctx.h, plan.h, _ptr(peer_nbr), arr, rows, len(x_ptrs), int(rank), _ptr(w), ctypes.byref(e),
+    ctx = ctx or c.ctx
+    ctx.check(ctx.lib.t2sc_subm_conv_peers_part(ctx.h, plan.h, _ptr(peer_nbr), arr, rows, len(x_ptrs), int(rank), _ptr(w), ctypes.byref(e),
                                                     _ptr(y), _DT[x_dtype], Ci, Co, _lib.PART[part]))
     return y
 
@@ -439,6 +443,22 @@ def row_epilogue(x: torch.Tensor, *, ln=None, act=None, residual=None, out=None)
     y = out if out is not None else torch.empty_like(x)
     e, keep = _epilogue(x.shape[1], x.dtype, None, ln, act, residual, None)
     ctx.check(ctx.lib.t2sc_row_epilogue(ctx.h, _ptr(x), ctypes.byref(e), _ptr(y), x.shape[0], x.shape[1], _DT[x.dtype]))
+    return y
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None, *, ln=None, act=None, residual=None, out=None) -> torch.Tensor:
+    """y = x . w^T + b (src/gemm.cu:25-64) with what the decoder's ConvNeXt block strings around its two Linear layers fused
+    (src/sdec.cu:62-65): ``act`` ("silu" after the first), ``residual`` (``add_`` after the second), ``ln``.  x [n,Ci],
+    w [Co,Ci], fp16 / bf16, on the conv's tcgen05 kernel."""
+    _chk(x, "x", None, 2); _chk(w, "w", x.dtype, 2)
+    if w.shape[1] != x.shape[1]:
+        raise T2scError(-1, f"linear shapes: w {tuple(w.shape)} does not match x {tuple(x.shape)}")
+    ctx = context(x.device)
+    Co = w.shape[0]
+    y = out if out is not None else torch.empty((x.shape[0], Co), dtype=x.dtype, device=x.device)
+    e, keep = _epilogue(Co, x.dtype, b, ln, act, residual, None)
+    ctx.check(ctx.lib.t2sc_linear(ctx.h, _ptr(x), _ptr(w), ctypes.byref(e), _ptr(y), _DT[x.dtype], x.shape[0], x.shape[1], Co))
+    ctx.keep = keep           # alive until this context's next linear (the kernel runs on the context's stream)
     return y
 
 
