@@ -76,6 +76,10 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
   const void** peer_base = (const void**)(tmem_slot + 4);      // the peers' array addresses (PEERS only)
   uint32_t* tab_remote = (uint32_t*)(peer_base + 8);           // PEERS: [NTAB][2 index warps][32 taps] does the tap read any row of a peer?
   uint32_t* peer_rows = tab_remote + NTAB * 64;                // PEERS: rows of every peer's array (bounds of the map entries)
+  // epilogue staging: LayerNorm gamma / beta of the row, and per epilogue warp the bias values of its current item
+  uint8_t* epi_s = (uint8_t*)(((uintptr_t)(smem + S * STAGE + aux_bytes(MH) - epi_bytes(MH)) + 15) & ~(uintptr_t)15);
+  float* gamma_s = (float*)epi_s; float* beta_s = gamma_s + 256;
+  T* bias_s = (T*)(beta_s + 256);                              // [4 * MH epilogue warps][256]
 
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * S, bar_accf = bar_empty + 8 * S, bar_acce = bar_accf + 16,
@@ -92,6 +96,9 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
     if (PEERS) for (int r = 0; r < 8; r++) { peer_base[r] = a.xp[r]; peer_rows[r] = a.xp_rows[r]; }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (a.ep.ln) {        // the whole row is one accumulator (n_cot == 1): column = index
+    for (int i = threadIdx.x; i < BN; i += blockDim.x) { gamma_s[i] = a.ep.gamma ? a.ep.gamma[i] : 1.f; beta_s[i] = a.ep.beta ? a.ep.beta[i] : 0.f; }
   }
   if (warp == WARP_MMA) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
@@ -412,13 +419,20 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
       const int wcol0 = tile.wbase * a.Co + cot * BN;      // bias index of this item's first column
       int sp = 0, ss = 0;
       if (has_skip && orow >= 0) { int sv = a.ep.skip_src[orow]; sp = sv >> 3; ss = sv & 7; }
+      // this warp's copy of the item's bias values, in flight while it waits for the accumulator
+      T* const bias_w = bias_s + (warp - WARP_EPI0) * 256;
+      if (a.ep.bias) {
+        __syncwarp();                                     // the previous item's reads of the copy are done
+        if (lane < BN / 8) ((uint4*)bias_w)[lane] = __ldg((const uint4*)((const T*)a.ep.bias + wcol0) + lane);
+        __syncwarp();
+      }
       // warp-uniform (tcgen05.ld is warp-collective); after a wait was given up nothing more is read or signalled
       if (warp == WARP_EPI0 && lane == 0) trace(a, 4, 0, acc_it);
       if (!__all_sync(0xffffffffu, mbar_wait_t(bar_accf + 8 * buf, aph, abort_flag, a.status, 16, prof, w_accf))) break;
       if (warp == WARP_EPI0 && lane == 0) trace(a, 4, 1, acc_it);
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (MH * BN) + half * BN;
-      if (!diag(a, 64)) epilogue_row<BN, T>(a, taddr, orow, cot, wcol0, sp, ss);
+      if (!diag(a, 64)) epilogue_row<BN, T>(a, taddr, orow, cot, a.ep.bias ? bias_w : nullptr, gamma_s, beta_s, sp, ss);
       tc_fence_before();
       mbar_arrive(bar_acce + 8 * buf);
       if (warp == WARP_EPI0 && lane == 0) trace(a, 4, 2, acc_it);

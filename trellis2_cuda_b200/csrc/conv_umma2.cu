@@ -287,7 +287,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) k_conv_umma2(const __grid_consta
       if (!__all_sync(0xffffffffu, mbar_wait_cluster(bar_accf + 8 * buf, aph, abort_flag, a.status, 16))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * P_BN;
-      epilogue_row<P_BN, T>(a, taddr, orow, cot, wcol0, sp, ss);
+      epilogue_row<P_BN, T>(a, taddr, orow, cot, a.ep.bias ? (const T*)a.ep.bias + wcol0 : nullptr, a.ep.gamma, a.ep.beta, sp, ss);
       tc_fence_before();
       mbar_arrive_cluster(acce_leader + 8 * buf);
     }

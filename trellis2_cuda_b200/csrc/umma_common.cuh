@@ -41,7 +41,10 @@ __host__ __device__ constexpr int stage_bytes(int BN, int MH) { return MH * A_BY
 // per instruction and the gather warps read 16 rows of one tap, both without bank conflicts.
 __host__ __device__ constexpr int tab_pitch(int MH) { return MH * TILE_M + 1; }
 __host__ __device__ constexpr int tab_words(int MH) { return 27 * tab_pitch(MH); }
-__host__ __device__ constexpr int aux_bytes(int MH) { return NTAB * tab_words(MH) * 4 + 1024; }
+// Epilogue staging behind the tables and barriers: LayerNorm gamma and beta (fp32, up to 256 columns each) and one block of up
+// to 256 bias values per epilogue warp.
+__host__ __device__ constexpr int epi_bytes(int MH) { return 2048 + MH * 2048 + 16; }
+__host__ __device__ constexpr int aux_bytes(int MH) { return NTAB * tab_words(MH) * 4 + 1024 + epi_bytes(MH); }
 __host__ __device__ constexpr int num_stages(int BN, int MH, int U = 1) {
   int s = (SMEM_BUDGET - 1024 - aux_bytes(MH)) / (U * stage_bytes(BN, MH));
 #ifdef T2SC_MAX_STAGES
@@ -234,28 +237,32 @@ template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t v) { retu
 template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v)); }
 
 
-// Fused epilogue of one output row (this thread's TMEM lane) over the BN accumulator columns at `taddr`:
-// round -> + bias -> LayerNorm -> activation -> + residual -> + skip, each rounded to the storage type, then store.
-// All lanes of the warp must call it (tcgen05.ld is warp-collective); orow < 0 loads but does not store.
-// 32 consecutive bias values (16-byte aligned: wcol0 is a multiple of 32) added with the storage rounding
+// The epilogue keeps a 32-column block of a row as 16 packed pairs of the storage type between its ops: an op unpacks
+// (shifts), computes in fp32 and packs again (ONE conversion per pair), which is the storage rounding the reference's
+// separate kernels apply after every op, and the block is stored as it stands.
 template <class T>
-__device__ __forceinline__ void add_bias32(float* h, const T* bias) {
-  const uint4* bp = (const uint4*)bias;
+__device__ __forceinline__ void add_packed32(uint32_t* hp, const uint4* src) {       // hp += 32 values of the storage type at src (16-byte aligned)
 #pragma unroll
   for (int g = 0; g < 4; g++) {
-    const uint4 bv = __ldg(bp + g); const uint32_t* w32 = (const uint32_t*)&bv;
+    const uint4 bv = src[g]; const uint32_t* w32 = (const uint32_t*)&bv;
 #pragma unroll
     for (int e = 0; e < 4; e++) {
-      const float2 f = unpack2<T>(w32[e]);
-      h[g * 8 + e * 2] = rnd<T>(h[g * 8 + e * 2] + f.x); h[g * 8 + e * 2 + 1] = rnd<T>(h[g * 8 + e * 2 + 1] + f.y);
+      const float2 f = unpack2<T>(w32[e]), h = unpack2<T>(hp[g * 4 + e]);
+      hp[g * 4 + e] = pack2<T>(h.x + f.x, h.y + f.y);
     }
   }
 }
 
+// Fused epilogue of one output row (this thread's TMEM lane) over the BN accumulator columns at `taddr`, in 32-column blocks:
+// round -> + bias -> LayerNorm -> activation -> + residual -> + skip, each rounded to the storage type, then stores.
+// All lanes of the warp must call it (tcgen05.ld is warp-collective); orow < 0 loads but does not store.
+// bias points at the item's first column (or is null); gamma / beta at the row's first column (LayerNorm only, may be null).
+// The kernels hand in copies in shared memory: a per-element load from global memory here costs its full latency once per
+// block, because one epilogue warp per scheduler has nothing else to run meanwhile.
 template <int BN, class T>
-__device__ __forceinline__ void epilogue_row(const ConvArgs& a, uint32_t taddr, int orow, int cot, int wcol0, int sp, int ss) {
+__device__ __forceinline__ void epilogue_row(const ConvArgs& a, uint32_t taddr, int orow, int cot, const T* bias, const float* gamma, const float* beta, int sp, int ss) {
   T* y = (T*)a.y;
-  const T* bias = (const T*)a.ep.bias; const T* res = (const T*)a.ep.residual; const T* skx = (const T*)a.ep.skip_x;
+  const T* res = (const T*)a.ep.residual; const T* skx = (const T*)a.ep.skip_x;
   float mean = 0.f, rstd = 1.f;
   if (a.ep.ln) {      // whole row lives in this accumulator (n_cot == 1)
     // ONE statistics pass over TMEM (every tcgen05.ld round trip counts: at Co <= 128 the epilogue is as long as the tile's
@@ -264,13 +271,17 @@ __device__ __forceinline__ void epilogue_row(const ConvArgs& a, uint32_t taddr, 
     float s1 = 0.f, s2 = 0.f, K = 0.f;
     for (int cc = 0; cc < BN / 32; cc++) {
       uint32_t r[32]; tc_ld32(taddr + cc * 32, r); tc_wait_ld();
-      float h[32];
+      uint32_t hp[16];
 #pragma unroll
-      for (int i = 0; i < 32; i++) h[i] = rnd<T>(__uint_as_float(r[i]));
-      if (bias) add_bias32<T>(h, bias + wcol0 + cc * 32);
-      if (cc == 0) K = h[0];
+      for (int i = 0; i < 16; i++) hp[i] = pack2<T>(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+      if (bias) add_packed32<T>(hp, (const uint4*)(bias + cc * 32));
+      if (cc == 0) K = unpack2<T>(hp[0]).x;
 #pragma unroll
-      for (int i = 0; i < 32; i++) { const float d = h[i] - K; s1 += d; s2 = fmaf(d, d, s2); }
+      for (int i = 0; i < 16; i++) {
+        const float2 h = unpack2<T>(hp[i]);
+        const float d0 = h.x - K, d1 = h.y - K;
+        s1 += d0 + d1; s2 = fmaf(d0, d0, fmaf(d1, d1, s2));
+      }
     }
     const float m1 = s1 / (float)BN;
     mean = K + m1;
@@ -298,50 +309,45 @@ __device__ __forceinline__ void epilogue_row(const ConvArgs& a, uint32_t taddr, 
     tc_wait_ld();
     if (orow < 0) continue;
     const int col = cot * BN + cc * 32;
-    float h[32];
+    uint32_t hp[16];
 #pragma unroll
-    for (int i = 0; i < 32; i++) h[i] = rnd<T>(__uint_as_float(r[i]));
-    if (bias) add_bias32<T>(h, bias + wcol0 + cc * 32);
+    for (int i = 0; i < 16; i++) hp[i] = pack2<T>(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+    if (bias) add_packed32<T>(hp, (const uint4*)(bias + cc * 32));
     if (a.ep.ln) {
 #pragma unroll
-      for (int i = 0; i < 32; i++) {
-        float v = rstd * (h[i] - mean);
-        if (a.ep.gamma) v = a.ep.gamma[col + i] * v;
-        if (a.ep.beta) v = v + a.ep.beta[col + i];
-        h[i] = rnd<T>(v);
+      for (int i = 0; i < 16; i++) {
+        const float2 h = unpack2<T>(hp[i]);
+        float v0 = rstd * (h.x - mean), v1 = rstd * (h.y - mean);
+        if (gamma) { v0 *= gamma[cc * 32 + 2 * i]; v1 *= gamma[cc * 32 + 2 * i + 1]; }
+        if (beta) { v0 += beta[cc * 32 + 2 * i]; v1 += beta[cc * 32 + 2 * i + 1]; }
+        hp[i] = pack2<T>(v0, v1);
       }
     }
     if (a.ep.act == T2SC_ACT_SILU) {          // one branch per block, not per element
 #pragma unroll
-      for (int i = 0; i < 32; i++) h[i] = rnd<T>(__fdividef(h[i], 1.f + __expf(-h[i])));
+      for (int i = 0; i < 16; i++) {
+        const float2 h = unpack2<T>(hp[i]);
+        hp[i] = pack2<T>(__fdividef(h.x, 1.f + __expf(-h.x)), __fdividef(h.y, 1.f + __expf(-h.y)));
+      }
     } else if (a.ep.act) {
 #pragma unroll
-      for (int i = 0; i < 32; i++) h[i] = rnd<T>(act_apply(h[i], a.ep.act));
-    }
-    if (rp) {
-#pragma unroll
-      for (int g = 0; g < 4; g++) {
-        const uint32_t* w32 = (const uint32_t*)&rcur[g];
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-          float2 f = unpack2<T>(w32[e]);
-          h[g * 8 + e * 2] = rnd<T>(h[g * 8 + e * 2] + f.x); h[g * 8 + e * 2 + 1] = rnd<T>(h[g * 8 + e * 2 + 1] + f.y);
-        }
+      for (int i = 0; i < 16; i++) {
+        const float2 h = unpack2<T>(hp[i]);
+        hp[i] = pack2<T>(act_apply(h.x, a.ep.act), act_apply(h.y, a.ep.act));
       }
     }
+    if (rp) add_packed32<T>(hp, rcur);
     if (skx) {
       const T* sx = skx + (i64)sp * a.ep.skip_cin + ss * (a.ep.skip_cin / 8);
 #pragma unroll
-      for (int i = 0; i < 32; i++) h[i] = rnd<T>(h[i] + to_f<T>(sx[(col + i) / a.ep.skip_rep]));
+      for (int i = 0; i < 16; i++) {
+        const float2 h = unpack2<T>(hp[i]);
+        hp[i] = pack2<T>(h.x + to_f<T>(sx[(col + 2 * i) / a.ep.skip_rep]), h.y + to_f<T>(sx[(col + 2 * i + 1) / a.ep.skip_rep]));
+      }
     }
     uint4* yp = (uint4*)(y + (i64)orow * a.Co + col);
 #pragma unroll
-    for (int g = 0; g < 4; g++) {
-      uint4 o;
-      o.x = pack2<T>(h[g * 8 + 0], h[g * 8 + 1]); o.y = pack2<T>(h[g * 8 + 2], h[g * 8 + 3]);
-      o.z = pack2<T>(h[g * 8 + 4], h[g * 8 + 5]); o.w = pack2<T>(h[g * 8 + 6], h[g * 8 + 7]);
-      yp[g] = o;
-    }
+    for (int g = 0; g < 4; g++) yp[g] = make_uint4(hp[g * 4], hp[g * 4 + 1], hp[g * 4 + 2], hp[g * 4 + 3]);
   }
 }
 
