@@ -650,6 +650,71 @@ def run_cfg4(args, rank, world, local_rank, dev):
     print(json.dumps(line), flush=True)
 
 
+def run_mlp(args, rank, world, local_rank, dev):
+    """The MLP half of the decoder's ConvNeXt block (src/sdec.cu:62-65 of trellis2-cuda: Linear C -> 4C, SiLU, Linear 4C -> C, add_)
+    on the conv kernel (t2sc_linear, fused tails), at the row counts and widths of configurations 2-4; beside it the same
+    four ops through torch (cuBLAS GEMM + separate elementwise kernels), which is what the reference's gemm.cu / ops.cu do."""
+    import trellis2_cuda_b200 as sp
+    ctx = sp.context(dev)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    F = torch.nn.functional
+    sampler = ClockSampler(visible_gpu_index(local_rank))
+    sampler.start()
+    t0 = time.perf_counter()
+    l0 = ctx.launch_count()
+    rows, flops_total, ms_total = [], 0.0, 0.0
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        a, b = ev(), ev()
+        a.record()
+        for _ in range(args.steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / args.steps
+
+    sampler.wait_first_sample()
+    for n, C in ((217821, 256), (201165, 128), (727949, 64)):
+        g = torch.Generator(device="cpu").manual_seed(C)
+        x = torch.randn(n, C, generator=g).to(torch.bfloat16).to(dev)           # 2 x n x 5C x 2 bytes per block: larger than the L2 at every size
+        w1 = (torch.randn(4 * C, C, generator=g) / C ** 0.5).to(torch.bfloat16).to(dev)
+        w2 = (torch.randn(C, 4 * C, generator=g) / (4 * C) ** 0.5).to(torch.bfloat16).to(dev)
+        b1, b2 = torch.zeros(4 * C, dtype=torch.bfloat16, device=dev), torch.zeros(C, dtype=torch.bfloat16, device=dev)
+        h, y = torch.empty(n, 4 * C, dtype=torch.bfloat16, device=dev), torch.empty(n, C, dtype=torch.bfloat16, device=dev)
+
+        def ours():
+            sp.linear(x, w1, b1, act="silu", out=h)
+            sp.linear(h, w2, b2, residual=x, out=y)
+
+        def lib():
+            return F.linear(F.silu(F.linear(x, w1, b1)), w2, b2).add_(x)
+
+        ms, ms_lib = timed(ours), timed(lib)
+        fl = 2.0 * n * C * 4 * C * 2
+        byt = (n * C * 2 + n * 4 * C * 2 * 2 + n * C * 2 * 2) + 2 * 4 * C * C * 2      # x, h written and read, residual, y, weights
+        rows.append({"rows": n, "C": C, "ms": ms, "tflops": fl / (ms * 1e-3) / 1e12, "gb_s_algorithmic": byt / (ms * 1e-3) / 1e9,
+                     "library_gemm_ms": ms_lib, "vs_library": ms_lib / ms})
+        flops_total += fl; ms_total += ms
+    launches = ctx.launch_count() - l0
+    t1 = time.perf_counter()
+    ctx.device_status()
+    clocks = sampler.stop(t0, t1)
+    pk, pk_src = peaks()
+    line = {"metric": "dense MLP TFLOP/s", "value": flops_total / (ms_total * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_total, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "mlp: Linear C -> 4C + SiLU, Linear 4C -> C + residual (the ConvNeXt MLP of the decoder) at 217,821 x 256, 201,165 x 128, 727,949 x 64",
+                       "step": "two t2sc_linear calls per size", "l2": "inputs larger than L2 (activations of one block: 0.5 - 1.1 GB)"},
+            "sizes": rows,
+            "roofline": {"bound": "hbm", "achieved": min(r["gb_s_algorithmic"] for r in rows), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": min(r["gb_s_algorithmic"] for r in rows) / pk["hbm_gbs"], "traffic": None, "peak_source": f"{pk_src} copy bandwidth",
+                         "kernel": "k_conv_umma (dense rows), lowest of the sizes"},
+            "clocks": clocks, "gpu_launches": launches, "e2e": None}
+    print(json.dumps(line), flush=True)
+
+
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
     torch.cuda.set_device(local_rank)
@@ -663,6 +728,8 @@ def run_ours(args, rank, world, local_rank):
         return run_cfg3(args, rank, world, local_rank, dev)
     if args.workload == "cfg4":
         return run_cfg4(args, rank, world, local_rank, dev)
+    if args.workload == "mlp":
+        return run_mlp(args, rank, world, local_rank, dev)
     return run_single_conv(args, rank, world, local_rank, dev)
 
 
@@ -672,7 +739,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"])
+    ap.add_argument("--workload", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "mlp"])
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--channels", type=int, default=0, help="cfg1/cfg2: run the workload's geometry at this channel width instead of its own")
     ap.add_argument("--halo", default="nccl", choices=["p2p", "nccl"], help="cfg5: halo rows by peer-memory loads inside the conv, or by NCCL all-to-all")
@@ -680,7 +747,7 @@ def main():
     ap.add_argument("--no-sharded", action="store_true", help="N > 1: leave out the sharded cfg5 block")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.workload in ("cfg3", "cfg4", "cfg5"):
+    if args.workload in ("cfg3", "cfg4", "cfg5", "mlp"):
         args.steps = min(args.steps, 50)                # multi-ms steps: fifty of them time well and keep the run short
     rank, world, local_rank = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
