@@ -225,7 +225,7 @@ def measure(args, rank, world, local_rank, peaks, ClockSampler, visible_gpu_inde
             full = sp.build_neighbors(coords, want_sorted=False)
             xa1, xb1 = x_full.clone(), torch.empty_like(x_full)
             ms1 = []
-            for i in range(max(single_gpu_steps, 3) + 2):
+            for i in range(max(single_gpu_steps, 5) + 3):
                 s, e = ev(), ev()
                 s.record()
                 a, b = xa1, xb1
@@ -235,7 +235,7 @@ def measure(args, rank, world, local_rank, peaks, ClockSampler, visible_gpu_inde
                     a, b = b, a
                 e.record()
                 sync()
-                if i >= 2:
+                if i >= 3:
                     ms1.append(s.elapsed_time(e))
             single = sum(ms1) / len(ms1)
             ctx.device_status()
