@@ -123,27 +123,35 @@ __global__ void __launch_bounds__(256) k_brick_neighbors(const int4* __restrict_
         }
       }
     }
-    // offsets of this thread's brick along each axis: first offset d0 and count
-    const int x0 = sx ? ((x & 1) ? 1 : 0) : -1, xn = sx ? ((x & 1) ? 1 : 2) : ((x & 1) ? 2 : 1);
-    const int y0 = sy ? ((y & 1) ? 1 : 0) : -1, yn = sy ? ((y & 1) ? 1 : 2) : ((y & 1) ? 2 : 1);
-    const int z0 = sz ? ((z & 1) ? 1 : 0) : -1, zn = sz ? ((z & 1) ? 1 : 2) : ((z & 1) ? 2 : 1);
-    for (int ix = 0; ix < xn; ix++)
-      for (int iy = 0; iy < yn; iy++)
-        for (int iz = 0; iz < zn; iz++) {
-          const int dx = x0 + ix, dy = y0 + iy, dz = z0 + iz;
-          const int cx = x + dx, cy = y + dy, cz = z + dz;
-          const int v = (dx + 1) * 9 + (dy + 1) * 3 + (dz + 1);                         // src/spconv.cu:27
-          uint32_t r = NBR_EMPTY;
-          if (cx >= 0 && cx < W && cy >= 0 && cy < H && cz >= 0 && cz < D) r = bv.v[(cx & 1) | ((cy & 1) << 1) | ((cz & 1) << 2)];
-          nbr[row * 27 + v] = r;
-          if (r != NBR_EMPTY) g |= 1u << v;
-        }
+    // The brick's 8 cells, by their fixed position e = (ex, ey, ez) in the brick: cell (2 bx + ex, 2 by + ey, 2 bz + ez) is the
+    // row's tap (dx, dy, dz) when every offset is in -1 .. 1.  Every tap of the row lies in exactly one of the 8 bricks, so
+    // the 8 threads write the row's 27 entries between them, and the cell's value is read with a constant index.  What
+    // depends on one axis only is worked out once per axis: is the offset a tap offset (and the cell inside the grid), and
+    // its share of the tap number v = (dx + 1) * 9 + (dy + 1) * 3 + (dz + 1) (src/spconv.cu:27).
+    bool okx[2], oky[2], okz[2], inx[2], iny[2], inz[2]; int vx[2], vy[2], vz[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const int cx = 2 * bx + h, cy = 2 * by + h, cz = 2 * bz + h;
+      okx[h] = (unsigned)(cx - x + 1) <= 2u; vx[h] = (cx - x + 1) * 9; inx[h] = (unsigned)cx < (unsigned)W;
+      oky[h] = (unsigned)(cy - y + 1) <= 2u; vy[h] = (cy - y + 1) * 3; iny[h] = (unsigned)cy < (unsigned)H;
+      okz[h] = (unsigned)(cz - z + 1) <= 2u; vz[h] = cz - z + 1;       inz[h] = (unsigned)cz < (unsigned)D;
+    }
+    uint32_t* const out = nbr + row * 27;
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+      const int ex = e & 1, ey = (e >> 1) & 1, ez = e >> 2;
+      if (okx[ex] && oky[ey] && okz[ez]) {
+        const int v = vx[ex] + vy[ey] + vz[ez];
+        const uint32_t r = inx[ex] && iny[ey] && inz[ez] ? bv.v[e] : NBR_EMPTY;      // a neighbour outside the grid is absent (src/spconv.cu:28)
+        out[v] = r;
+        if (r != NBR_EMPTY) g |= 1u << v;
+      }
+    }
   }
   g |= __shfl_xor_sync(0xffffffffu, g, 1); g |= __shfl_xor_sync(0xffffffffu, g, 2); g |= __shfl_xor_sync(0xffffffffu, g, 4);
   if (live && t == 0) {
-    uint32_t b = g;
-#pragma unroll
-    for (int v = 1; v < 27; v++) b ^= g >> v;       // gray -> binary, src/spconv.cu:34
+    uint32_t b = g;                                 // gray -> binary (src/spconv.cu:34): XOR of all right shifts, as a prefix scan
+    b ^= b >> 16; b ^= b >> 8; b ^= b >> 4; b ^= b >> 2; b ^= b >> 1;
     gray[row] = (int)g;
     if (bin) bin[row] = (int)b;
   }

@@ -25,9 +25,8 @@ __device__ __forceinline__ uint32_t mask_key(uint32_t g) {
   uint32_t k = 0;
 #pragma unroll
   for (int v = 0; v < 27; v++) k |= ((g >> v) & 1u) << (26 - TAP_RANK[v]);
-  uint32_t b = k;
-#pragma unroll
-  for (int v = 1; v < 27; v++) b ^= k >> v;
+  uint32_t b = k;         // gray -> binary: the XOR of all right shifts, as a prefix scan
+  b ^= b >> 16; b ^= b >> 8; b ^= b >> 4; b ^= b >> 2; b ^= b >> 1;
   return b;
 }
 
@@ -38,20 +37,31 @@ template <class K>
 __global__ void k_plan_keys(const int* __restrict__ gray, const int* __restrict__ src, const uint32_t* __restrict__ nbr, uint32_t halo_from,
                             i64 m, i64 block_rows, int block_bits, int drop,
                             K* __restrict__ keys, int* __restrict__ iota, int* __restrict__ group_cnt) {
+  // group sizes: counted per CTA in shared memory first (millions of rows on eight counters in global memory were the
+  // whole time of this kernel)
+  __shared__ int s_cnt[8];
+  const bool grouped = src || halo_from;
+  if (grouped && threadIdx.x < 8) s_cnt[threadIdx.x] = 0;
+  if (grouped) __syncthreads();
   i64 i = blockIdx.x * (i64)blockDim.x + threadIdx.x;
-  if (i >= m) return;
-  int grp = 0; i64 nrow = i;
-  if (src) { int s = src[i]; grp = s & 7; nrow = s >> 3; }
-  else if (halo_from) {
-    const uint32_t* e = nbr + i * 27;
+  if (i < m) {
+    int grp = 0; i64 nrow = i;
+    if (src) { int s = src[i]; grp = s & 7; nrow = s >> 3; }
+    else if (halo_from) {
+      const uint32_t* e = nbr + i * 27;
 #pragma unroll 9
-    for (int v = 0; v < 27; v++) { const uint32_t r = __ldg(e + v); grp |= (r != NBR_EMPTY && r >= halo_from) ? 1 : 0; }
+      for (int v = 0; v < 27; v++) { const uint32_t r = __ldg(e + v); grp |= (r != NBR_EMPTY && r >= halo_from) ? 1 : 0; }
+    }
+    unsigned long long blk = (unsigned long long)(i / block_rows);
+    const unsigned long long k = ((unsigned long long)grp << (27 + block_bits)) | (blk << 27) | mask_key((uint32_t)gray[nrow]);
+    keys[i] = (K)(k >> drop);
+    iota[i] = (int)i;
+    if (grouped) atomicAdd(&s_cnt[grp], 1);
   }
-  unsigned long long blk = (unsigned long long)(i / block_rows);
-  const unsigned long long k = ((unsigned long long)grp << (27 + block_bits)) | (blk << 27) | mask_key((uint32_t)gray[nrow]);
-  keys[i] = (K)(k >> drop);
-  iota[i] = (int)i;
-  if (src || halo_from) atomicAdd(&group_cnt[grp], 1);
+  if (grouped) {
+    __syncthreads();
+    if (threadIdx.x < 8 && s_cnt[threadIdx.x]) atomicAdd(&group_cnt[threadIdx.x], s_cnt[threadIdx.x]);
+  }
 }
 
 // The neighbour map in tile order: table[t][v][j] = entry of tap v of the j-th row of tile t (for a subdivision plan: of
@@ -119,11 +129,23 @@ __global__ void __launch_bounds__(256) k_plan_tiles_table(const uint32_t* __rest
     }
   }
   uint32_t big = 0;         // the largest present entry: lets the bounds check skip its scan when every entry is in range
-  for (int e = threadIdx.x; e < TILE * 27; e += 256) {
-    const int j = e / 27, v = e - j * 27, nr = s_row[j];
-    uint32_t val = TABLE_ABSENT;
-    if (nr >= 0) { val = __ldg(nbr + (i64)nr * 27 + v); if (val == NBR_EMPTY) val = TABLE_ABSENT; else big = max(big, val); }
-    s_e[v * (TILE + 1) + j] = val;
+  // all of a thread's loads are issued before the first of them is used: one load latency per tile, not one per entry
+  constexpr int PER = (TILE * 27 + 255) / 256;
+  uint32_t val[PER];
+#pragma unroll
+  for (int k = 0; k < PER; k++) {
+    const int e = threadIdx.x + 256 * k;
+    val[k] = NBR_EMPTY;
+    if (e < TILE * 27) { const int j = e / 27, v = e - j * 27, nr = s_row[j]; if (nr >= 0) val[k] = __ldg(nbr + (i64)nr * 27 + v); }
+  }
+#pragma unroll
+  for (int k = 0; k < PER; k++) {
+    const int e = threadIdx.x + 256 * k;
+    if (e < TILE * 27) {
+      const int j = e / 27, v = e - j * 27;
+      if (val[k] == NBR_EMPTY) val[k] = TABLE_ABSENT; else big = max(big, val[k]);
+      s_e[v * (TILE + 1) + j] = val[k];
+    }
   }
   big = __reduce_max_sync(0xffffffffu, big);
   if ((threadIdx.x & 31) == 0 && big > *(volatile uint32_t*)max_entry) atomicMax(max_entry, big);
