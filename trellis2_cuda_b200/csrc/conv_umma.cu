@@ -118,6 +118,18 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
     return tiles[t];
   };
   const int nitems = ntiles * a.n_cot;
+  // Work items of this CTA.  Position g in the launch's item list is tile a.perm[g / n_cot] (the plan's tiles by falling
+  // tap count, within windows of a few rounds on large maps) and column slab g % n_cot; the CTAs take the positions round
+  // by round in alternating direction, so that the CTA with the longest tile of one round gets the shortest of the next.
+  // Tiles differ 9..27 in taps: taken in plan order the busiest SM had 14 % more taps than the mean on a 1,702-tile map
+  // (measured: 6.5 % of the conv's time there, 2 % on 67,176 tiles).  By tap count WITHOUT the alternation the same CTA
+  // gets the longest tile of every round (11 % slower on 67,176 tiles).
+  auto item_at = [&](int k) {
+    const int g = k * (int)gridDim.x + ((k & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
+    return g < nitems ? g : -1;
+  };
+  auto tidx_of = [&](int item) { const int t = item / a.n_cot; return (dense || !a.perm) ? t : a.perm[tile0 + t] - tile0; };
+  auto tile_of = [&](int item) { return tile_at(tidx_of(item)); };
 
   if (warp < 4 || (G == 2 && warp >= warp_group2(MH))) {
     // ===================================================================== A producer: gather rows into the swizzled tile
@@ -128,10 +140,12 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
     uint32_t it = 0, tt = 0;
     bool alive = true;
     const bool prof = diag(a, 8); long long w_idx = 0, w_empty = 0, t_role = clock64();
-    PlanTile tile_next = blockIdx.x < nitems ? tile_at(blockIdx.x / a.n_cot) : PlanTile{};
-    for (int item = blockIdx.x; item < nitems; item += gridDim.x, tt++) {
+    int item_n = item_at(0);
+    PlanTile tile_next = item_n >= 0 ? tile_of(item_n) : PlanTile{};
+    for (int k = 0; item_n >= 0; k++, tt++) {
       const PlanTile tile = tile_next;
-      if (item + (int)gridDim.x < nitems) tile_next = tile_at((item + gridDim.x) / a.n_cot);     // in flight while this tile is gathered
+      item_n = item_at(k + 1);
+      if (item_n >= 0) tile_next = tile_of(item_n);     // in flight while this tile is gathered
       const uint32_t buf = tt % NTAB;
       // Every gather warp waits for every tile's table, also one that has none of the tile's units (G == 2): a warp can
       // then never release a buffer twice within one phase of its barrier.
@@ -220,11 +234,13 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
     if (lane == 0) {
       uint32_t it = 0;
       bool alive = true;        // false once a wait was given up: nothing more is loaded or signalled
-      PlanTile tile_next = blockIdx.x < nitems ? tile_at(blockIdx.x / a.n_cot) : PlanTile{};
-      for (int item = blockIdx.x; item < nitems && alive; item += gridDim.x) {
-        const int tile_id = item / a.n_cot, cot = item - tile_id * a.n_cot;
+      int item_n = item_at(0);
+      PlanTile tile_next = item_n >= 0 ? tile_of(item_n) : PlanTile{};
+      for (int k = 0; item_n >= 0 && alive; k++) {
+        const int cot = item_n % a.n_cot;
         const PlanTile tile = tile_next;
-        if (item + (int)gridDim.x < nitems) tile_next = tile_at((item + gridDim.x) / a.n_cot);
+        item_n = item_at(k + 1);
+        if (item_n >= 0) tile_next = tile_of(item_n);
         const int wrow = tile.wbase * a.Co + cot * BN;
         const int nunits = __popc(tile.mask) * nchunk;
         uint32_t mk = tile.mask;
@@ -248,7 +264,7 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
             if (++c == nchunk) { c = 0; mk &= mk - 1; }
           }
         }
-        trace(a, 1, 0, (uint32_t)((item - blockIdx.x) / gridDim.x));
+        trace(a, 1, 0, (uint32_t)k);
       }
     }
     __syncwarp();
@@ -256,14 +272,19 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
     // ===================================================================== neighbour-index table: one bulk copy per tile
     if (warp == WARP_IDX && lane == 0 && !dense) {
       uint32_t tt = 0;
-      for (int item = blockIdx.x; item < nitems; item += gridDim.x, tt++) {
+      int item_n = item_at(0);
+      int tidx_next = item_n >= 0 ? tidx_of(item_n) : 0;
+      for (int k = 0; item_n >= 0; k++, tt++) {
+        const int tidx = tidx_next;
+        item_n = item_at(k + 1);
+        if (item_n >= 0) tidx_next = tidx_of(item_n);      // the next tile's number is in flight while this table is fetched
         const uint32_t buf = tt % NTAB;
         trace(a, 2, 0, tt);
         if (!mbar_wait(bar_tfree + 8 * buf, ((tt / NTAB) & 1) ^ 1, abort_flag, a.status, 64)) break;
         trace(a, 2, 1, tt);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the gather warps' reads of this buffer come before the copy's writes
         mbar_arrive_expect_tx(bar_tready + 8 * buf, TABW * 4);
-        bulk_load(smem_u32(itab + buf * TABW), a.tnbr + (i64)(tile0 + item / a.n_cot) * TABW, TABW * 4, bar_tready + 8 * buf);
+        bulk_load(smem_u32(itab + buf * TABW), a.tnbr + (i64)(tile0 + tidx) * TABW, TABW * 4, bar_tready + 8 * buf);
         trace(a, 2, 3, tt);
       }
     }
@@ -286,12 +307,12 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
         if (j < tl.rows) { const int r = a.order[tl.start + j]; nr[i] = a.src ? (a.src[r] >> 3) : r; }
       }
     };
-    auto desc_of = [&](int item) { return item < nitems ? tile_at(item / a.n_cot) : PlanTile{}; };
+    auto desc_of = [&](int k) { const int it_ = item_at(k); return it_ >= 0 ? tile_of(it_) : PlanTile{}; };
     int nr[NR], nr_next[NR];
-    PlanTile tile_n0 = desc_of(blockIdx.x), tile_n1 = desc_of(blockIdx.x + gridDim.x);
+    PlanTile tile_n0 = desc_of(0), tile_n1 = desc_of(1);
     rows_of(tile_n0, nr);
-    for (int item = blockIdx.x; item < nitems; item += gridDim.x, tt++) {
-      const PlanTile tile_n2 = desc_of(item + 2 * gridDim.x);
+    for (int k = 0; item_at(k) >= 0; k++, tt++) {
+      const PlanTile tile_n2 = desc_of(k + 2);
       rows_of(tile_n1, nr_next);                               // in flight while this tile is served
       const uint32_t buf = tt % NTAB;
       // warp-uniform: the fill below is a warp-wide exchange of row numbers, and after a wait was given up nothing more
@@ -354,10 +375,12 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
       uint32_t it = 0, acc_it = 0;
       bool alive = true;        // false once a wait was given up: no more MMAs or commits
       const bool prof = diag(a, 8); long long w_full = 0, w_acc = 0, w_issue = 0, w_commit = 0, t_role = clock64();
-      PlanTile tile_next = blockIdx.x < nitems ? tile_at(blockIdx.x / a.n_cot) : PlanTile{};
-      for (int item = blockIdx.x; item < nitems && alive; item += gridDim.x, acc_it++) {
+      int item_n = item_at(0);
+      PlanTile tile_next = item_n >= 0 ? tile_of(item_n) : PlanTile{};
+      for (int k = 0; item_n >= 0 && alive; k++, acc_it++) {
         const PlanTile tile = tile_next;
-        if (item + (int)gridDim.x < nitems) tile_next = tile_at((item + gridDim.x) / a.n_cot);
+        item_n = item_at(k + 1);
+        if (item_n >= 0) tile_next = tile_of(item_n);
         const uint32_t buf = acc_it % NB, aph = (acc_it / NB) & 1;
         trace(a, 3, 0, acc_it);
         alive &= mbar_wait_t(bar_acce + 8 * buf, aph ^ 1, abort_flag, a.status, 4, prof, w_acc);
@@ -409,11 +432,13 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
     const int q = warp & 3, half = (warp - WARP_EPI0) >> 2, j = half * TILE_M + q * 32 + lane;
     uint32_t acc_it = 0;
     const bool prof = diag(a, 8); long long w_accf = 0, t_role = clock64();
-    PlanTile tile_next = blockIdx.x < nitems ? tile_at(blockIdx.x / a.n_cot) : PlanTile{};
-    for (int item = blockIdx.x; item < nitems; item += gridDim.x, acc_it++) {
-      const int tile_id = item / a.n_cot, cot = item - tile_id * a.n_cot;
+    int item_n = item_at(0);
+    PlanTile tile_next = item_n >= 0 ? tile_of(item_n) : PlanTile{};
+    for (int k = 0; item_n >= 0; k++, acc_it++) {
+      const int cot = item_n % a.n_cot;
       const PlanTile tile = tile_next;
-      if (item + (int)gridDim.x < nitems) tile_next = tile_at((item + gridDim.x) / a.n_cot);
+      item_n = item_at(k + 1);
+      if (item_n >= 0) tile_next = tile_of(item_n);
       const uint32_t buf = acc_it % NB, aph = (acc_it / NB) & 1;
       const int orow = j < tile.rows ? (dense ? tile.start + j : a.order[tile.start + j]) : -1;
       const int wcol0 = tile.wbase * a.Co + cot * BN;      // bias index of this item's first column
@@ -563,6 +588,7 @@ int conv_umma_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const 
   for (int r = 0; r < 8; r++) { args.xp[r] = r < n_peers ? x_peers[r] : nullptr; args.xp_rows[r] = r < n_peers ? (uint32_t)rows_peers[r] : 0u; }
   if (n_peers == 0) { int prc = plan_table_prepare(ctx, const_cast<t2sc_plan*>(plan), n_in); if (prc != T2SC_OK) return prc; }
   args.tnbr = plan->tnbr;
+  args.perm = plan->perm;
   args.x = x; args.y = y; args.nbr = peer_nbr ? peer_nbr : plan->nbr; args.order = plan->order; args.src = plan->src;
   args.tiles = plan->tiles; args.tile_lo = tile_part(plan, part).lo; args.tile_hi = tile_part(plan, part).hi; args.status = ctx->status;
   args.Ci = Ci; args.Co = Co; args.n_cot = Co / BN; args.is_bf16 = dtype == T2SC_BF16; args.ep = ep;

@@ -77,12 +77,12 @@ __global__ void __launch_bounds__(256) k_plan_tiles_table(const uint32_t* __rest
                                                           const int* __restrict__ order, const int* __restrict__ group_cnt, int ngroups, int split,
                                                           i64 m, PlanTile* __restrict__ tiles, int* __restrict__ bounds,
                                                           unsigned long long* __restrict__ stats, uint32_t* __restrict__ table,
-                                                          uint32_t* __restrict__ max_entry) {
+                                                          uint32_t* __restrict__ max_entry, int* __restrict__ hist, int win) {
   const int t = blockIdx.x;
   __shared__ int s_row[TILE];
   __shared__ uint32_t s_e[27 * (TILE + 1)];
   __shared__ uint32_t s_or;
-  __shared__ int s_act;
+  __shared__ int s_act, s_part;
   PlanTile tile;
   if constexpr (HEADER) {
     // first row / first tile of every group; a group's tiles never mix with another's
@@ -97,7 +97,10 @@ __global__ void __launch_bounds__(256) k_plan_tiles_table(const uint32_t* __rest
     }
     if (t == 0 && threadIdx.x == 0) { bounds[0] = 0; bounds[1] = split ? first_boundary : tl; bounds[2] = tl; }
     if (!mine) return;
-    if (threadIdx.x == 0) { s_or = 0; s_act = 0; }
+    if (threadIdx.x == 0) {       // this tile's bin row in the tap-count histogram: (window of `win` tiles within its part, part)
+      const int part = (split && g >= 1) ? 1 : 0;
+      s_or = 0; s_act = 0; s_part = (((t - (part ? first_boundary : 0)) / win) * 2 + part) * 32;
+    }
     tile = PlanTile{start, rows, split ? 0 : g, 0};      // wbase holds the child slot (the conv multiplies by Co); the two parts of a split plan share one weight set
   } else {
     if (t >= bounds[2]) return;
@@ -126,6 +129,7 @@ __global__ void __launch_bounds__(256) k_plan_tiles_table(const uint32_t* __rest
       tiles[t] = tile;
       atomicAdd(&stats[0], (unsigned long long)tile.rows * __popc(mask));
       atomicAdd(&stats[1], (unsigned long long)s_act);
+      atomicAdd(&hist[s_part + __popc(mask)], 1);       // tiles of this window and part with this many taps (k_plan_perm)
     }
   }
   uint32_t big = 0;         // the largest present entry: lets the bounds check skip its scan when every entry is in range
@@ -157,6 +161,24 @@ __global__ void __launch_bounds__(256) k_plan_tiles_table(const uint32_t* __rest
   }
 }
 
+// perm[position] = tile.  Within every window of `win` consecutive tiles of a part ([b0,b1) and [b1,b2)) the tiles come by
+// falling tap count; windows keep the plan's order, because a plan over a large map sorts inside runs of caller rows to
+// keep the gathers of concurrently running tiles L2-local (win = a few rounds of the SMs; for a map sorted as one block
+// the window is the whole part).  hist[(window * 2 + part) * 32 + taps] holds the tile counts (k_plan_tiles_table),
+// cursor[] the next free slot of each bin.  Which of two tiles with the same tap count comes first is left to the order
+// of the atomics: it changes who computes a tile, never a result.
+__global__ void k_plan_perm(const PlanTile* __restrict__ tiles, const int* __restrict__ bounds, const int* __restrict__ hist,
+                            int* __restrict__ cursor, int win, int* __restrict__ perm) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= bounds[2]) return;
+  const int part = t >= bounds[1] ? 1 : 0, start = part ? bounds[1] : 0;
+  const int w = (t - start) / win, bin = (w * 2 + part) * 32;
+  const int taps = __popc(tiles[t].mask);
+  int before = 0;
+  for (int b = 27; b > taps; b--) before += hist[bin + b];
+  perm[start + w * win + before + atomicAdd(&cursor[bin + taps], 1)] = t;
+}
+
 // entries at or above n_in (the rows of the feature array) become absent and are reported (status bit 8)
 __global__ void k_plan_table_check(uint32_t* __restrict__ table, const int* __restrict__ ntiles, int per_tile, uint32_t n_in, int* status,
                                    const uint32_t* __restrict__ max_entry) {
@@ -171,15 +193,20 @@ __global__ void k_plan_table_check(uint32_t* __restrict__ table, const int* __re
 }
 
 template <bool HEADER>
-int plan_tiles_table(t2sc_ctx* ctx, t2sc_plan* p, const int32_t* gray, const int* gcnt, int ngroups) {
+int plan_tiles_table(t2sc_ctx* ctx, t2sc_plan* p, const int32_t* gray, const int* gcnt, int ngroups, int* hist = nullptr, int win = 1) {
   if (p->n_out == 0) return T2SC_OK;
   if (p->tile_rows == 128)
     k_plan_tiles_table<128, HEADER><<<(unsigned)p->max_tiles, 256, 0, ctx->stream>>>(p->nbr, gray, p->src, p->order, gcnt, ngroups, p->split ? 1 : 0, p->n_out,
-                                                                                       p->tiles, p->bounds, p->stats, p->tnbr, (uint32_t*)(p->meta + 11));
+                                                                                       p->tiles, p->bounds, p->stats, p->tnbr, (uint32_t*)(p->meta + 11), hist, win);
   else
     k_plan_tiles_table<256, HEADER><<<(unsigned)p->max_tiles, 256, 0, ctx->stream>>>(p->nbr, gray, p->src, p->order, gcnt, ngroups, p->split ? 1 : 0, p->n_out,
-                                                                                       p->tiles, p->bounds, p->stats, p->tnbr, (uint32_t*)(p->meta + 11));
+                                                                                       p->tiles, p->bounds, p->stats, p->tnbr, (uint32_t*)(p->meta + 11), hist, win);
   T2_LAUNCHED(ctx);
+  if (HEADER) {
+    const i64 bins = (cdiv_i(p->max_tiles, win) + 1) * 64;
+    k_plan_perm<<<(unsigned)cdiv_i(p->max_tiles, 256), 256, 0, ctx->stream>>>(p->tiles, p->bounds, hist, hist + bins, win, p->perm);
+    T2_LAUNCHED(ctx);
+  }
   return T2SC_OK;
 }
 
@@ -232,6 +259,7 @@ static int plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_t* gray, 
 #define PL(call) do { if ((e = (call)) != cudaSuccess) return fail(e); } while (0)
   PL(t2_alloc(ctx, &p->order, (size_t)m));
   PL(t2_alloc(ctx, &p->tiles, (size_t)p->max_tiles));
+  PL(t2_alloc(ctx, &p->perm, (size_t)p->max_tiles));
   PL(t2_alloc(ctx, &p->tnbr, (size_t)p->max_tiles * 27 * tile_rows));
   // one small block, one memset: group counts [0..8), part bounds [8..11), largest map entry [11], tap statistics (two u64) from int 12
   PL(t2_alloc(ctx, &p->meta, 16));
@@ -267,7 +295,14 @@ static int plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_t* gray, 
       PL(scratch.get(&tmp, tb));
       PL(cub::DeviceRadixSort::SortPairs(tmp, tb, keys, keys2, iota, p->order, (int)m, 0, key_bits, ctx->stream));
     }
-    if (plan_tiles_table<true>(ctx, p, gray, p->meta, ngroups) != T2SC_OK) return fail(cudaGetLastError());
+    // The order the conv's CTAs take the tiles in (k_plan_perm): by tap count within windows of four rounds of the SMs when
+    // the rows were sorted inside runs (large maps), within the whole part when they were sorted as one block.
+    const int win = block_rows >= m ? (1 << 30) : 4 * ctx->num_sms;
+    const i64 bins = (cdiv_i(p->max_tiles, win) + 1) * 64;
+    int* hist = nullptr;
+    PL(scratch.get(&hist, (size_t)(2 * bins)));
+    PL(cudaMemsetAsync(hist, 0, (size_t)(2 * bins) * sizeof(int), ctx->stream));
+    if (plan_tiles_table<true>(ctx, p, gray, p->meta, ngroups, hist, win) != T2SC_OK) return fail(cudaGetLastError());
   }
 #undef PL
   *out = p;
@@ -307,7 +342,7 @@ extern "C" int t2sc_plan_destroy(t2sc_ctx* ctx, t2sc_plan* p) {
   if (!p) return T2SC_OK;
   T2_REQ(ctx, ctx != nullptr, "null context");
   cudaSetDevice(ctx->device);
-  t2_free(ctx, p->order); t2_free(ctx, p->tiles); t2_free(ctx, p->tnbr); t2_free(ctx, p->meta);
+  t2_free(ctx, p->order); t2_free(ctx, p->tiles); t2_free(ctx, p->perm); t2_free(ctx, p->tnbr); t2_free(ctx, p->meta);
   delete p;
   return T2SC_OK;
 }

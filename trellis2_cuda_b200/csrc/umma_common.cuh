@@ -58,6 +58,7 @@ struct ConvArgs {
   const void* x; void* y; const uint32_t* nbr; const int* order; const int* src;
   const uint32_t* tnbr;     // the plan's map in tile order, [tile][27][rows]: one bulk copy per tile (not in the peer-memory form)
   const PlanTile* tiles; const int* tile_lo; const int* tile_hi; int* status;      // this launch covers tiles [*tile_lo, *tile_hi)
+  const int* perm;          // the plan's tiles of each part by falling tap count (positions -> tile numbers), or null: plan order
   int Ci, Co, n_cot, is_bf16;
   int npeers, self_rank;    // npeers > 0: map entries are (owner << PEER_SHIFT) | row and rows are read from xp[owner]; xp[self_rank] is local
   const void* xp[8];
@@ -85,6 +86,7 @@ static inline void diag_args(ConvArgs& args) {
   args.dbg_skip = 0;
   args.trace = nullptr;
   args.dense_rows = 0;
+  args.perm = nullptr;
   args.wait_limit = (int)(WAIT_LIMIT_CYCLES >> WAIT_LIMIT_SHIFT);
 #ifdef T2SC_DIAG
   static const int dbg_skip = [] { const char* e = getenv("T2SC_DEBUG_SKIP"); return e ? atoi(e) : 0; }();
