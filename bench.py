@@ -421,11 +421,19 @@ def run_single_conv(args, rank, world, local_rank, dev):
             "voxels_per_s": vox_all / (ms * 1e-3), "conv_only_tflops": flops_all / (conv_avg * 1e-3) / 1e12, "conv_ms": conv_avg,
             "map_and_plan_ms": ms - conv_avg,
             "roofline": roof, "clocks": clocks, "gpu_launches": launches,
-            "e2e": {"value": flops_all / (e2e_pipe_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_pipe_ms,
-                    "calls_in_flight": E2E_DEPTH, "equals_single_call_result": e2e_pipe_equal,
-                    "path": f"t2sc_subm_conv_host: pinned host buffers in, pinned host buffer out; {E2E_DEPTH} host threads, each with its own context, "
-                            "keep that many complete calls in flight (one call's copy out overlaps the next one's copy in and compute)",
-                    "one_call_at_a_time": {"value": flops_all / (e2e_total * 1e-3) / 1e12, "ms_per_step": e2e_total}}}
+            "e2e": None}
+    # Both ways of driving the host-buffer entry point are measured; the line's headline is the faster one on this host
+    # (with eight ranks on one host the copies of all ranks share its memory and PCIe roots, and more calls in flight
+    # per rank can lose).
+    piped = e2e_pipe_ms == e2e_pipe_ms and e2e_pipe_ms <= e2e_total
+    e2e_best = e2e_pipe_ms if piped else e2e_total
+    line["e2e"] = {"value": flops_all / (e2e_best * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_best,
+                   "calls_in_flight": E2E_DEPTH if piped else 1, "equals_single_call_result": e2e_pipe_equal,
+                   "path": "t2sc_subm_conv_host: pinned host buffers in, pinned host buffer out; the faster of one call at a time and "
+                           f"{E2E_DEPTH} host threads, each with its own context, keeping that many complete calls in flight (one call's copy out "
+                           "overlaps the next one's copy in and compute)",
+                   "one_call_at_a_time": {"value": flops_all / (e2e_total * 1e-3) / 1e12, "ms_per_step": e2e_total},
+                   f"calls_in_flight_{E2E_DEPTH}": {"value": flops_all / (e2e_pipe_ms * 1e-3) / 1e12, "ms_per_step": e2e_pipe_ms}}
     if sharded is not None:
         line["sharded"] = sharded
     if world == 1 and not args.profile:

@@ -40,9 +40,9 @@ struct t2sc_plan {
                                 // CTA copies into shared memory with one bulk copy)
   i64 table_n_in = -1;          // n_in the table was last checked against (-1: not yet)
   PlanTile* tiles = nullptr;    // [max_tiles]
-  int* perm = nullptr;          // [max_tiles]: positions -> tile numbers, the tiles of a part (of a window of a part, on large maps) by
-                                // falling tap count: the order the tcgen05 kernel's CTAs take them in, so that every SM gets
-                                // long and short tiles alike
+  int* perm = nullptr;          // [max_tiles]: positions -> tile numbers, each part's tiles by falling tap count: the order the
+                                // tcgen05 kernel's CTAs take them in, so that every SM gets long and short tiles alike
+  bool balanced = false;        // perm is filled (maps sorted as one block); large maps keep plan order for L2 locality
   int* meta = nullptr;          // device [16]: group counts, bounds, stats (one allocation, one memset)
   int* bounds = nullptr;        // = meta + 8, device [3]: {0, first boundary tile, realised tile count}; parts are [b0,b1) and [b1,b2)
   int* ntiles = nullptr;        // = bounds + 2: realised tile count (<= max_tiles)

@@ -118,14 +118,15 @@ __global__ void __launch_bounds__(num_threads(MH, G), 1) k_conv_umma(const __gri
     return tiles[t];
   };
   const int nitems = ntiles * a.n_cot;
-  // Work items of this CTA.  Position g in the launch's item list is tile a.perm[g / n_cot] (the plan's tiles by falling
-  // tap count, within windows of a few rounds on large maps) and column slab g % n_cot; the CTAs take the positions round
-  // by round in alternating direction, so that the CTA with the longest tile of one round gets the shortest of the next.
-  // Tiles differ 9..27 in taps: taken in plan order the busiest SM had 14 % more taps than the mean on a 1,702-tile map
-  // (measured: 6.5 % of the conv's time there, 2 % on 67,176 tiles).  By tap count WITHOUT the alternation the same CTA
-  // gets the longest tile of every round (11 % slower on 67,176 tiles).
+  // Work items of this CTA.  With a.perm (plans over maps sorted as one block, up to 262,144 rows): position g in the
+  // launch's item list is tile a.perm[g / n_cot] - the plan's tiles by falling tap count - and column slab g % n_cot, and the
+  // CTAs take the positions round by round in alternating direction, so that the CTA with the longest tile of one round
+  // gets the shortest of the next.  Tiles differ 9..27 in taps: taken in plan order the busiest SM had 14 % more taps than
+  // the mean on a 1,702-tile map (measured: 4-6 % of the conv's time there).  Without a.perm (large maps, whose plans sort
+  // inside runs of caller rows so that concurrently running tiles gather from the same part of the array): plan order,
+  // CTA b takes items b, b + grid, ...; permuting those tiles, even within windows of four rounds, cost 3 % on 67,176 tiles.
   auto item_at = [&](int k) {
-    const int g = k * (int)gridDim.x + ((k & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
+    const int g = k * (int)gridDim.x + ((k & 1) && a.perm ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
     return g < nitems ? g : -1;
   };
   auto tidx_of = [&](int item) { const int t = item / a.n_cot; return (dense || !a.perm) ? t : a.perm[tile0 + t] - tile0; };
@@ -588,7 +589,7 @@ int conv_umma_launch(t2sc_ctx* ctx, const t2sc_plan* plan, const void* x, const 
   for (int r = 0; r < 8; r++) { args.xp[r] = r < n_peers ? x_peers[r] : nullptr; args.xp_rows[r] = r < n_peers ? (uint32_t)rows_peers[r] : 0u; }
   if (n_peers == 0) { int prc = plan_table_prepare(ctx, const_cast<t2sc_plan*>(plan), n_in); if (prc != T2SC_OK) return prc; }
   args.tnbr = plan->tnbr;
-  args.perm = plan->perm;
+  args.perm = plan->balanced ? plan->perm : nullptr;
   args.x = x; args.y = y; args.nbr = peer_nbr ? peer_nbr : plan->nbr; args.order = plan->order; args.src = plan->src;
   args.tiles = plan->tiles; args.tile_lo = tile_part(plan, part).lo; args.tile_hi = tile_part(plan, part).hi; args.status = ctx->status;
   args.Ci = Ci; args.Co = Co; args.n_cot = Co / BN; args.is_bf16 = dtype == T2SC_BF16; args.ep = ep;

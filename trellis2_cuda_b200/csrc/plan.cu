@@ -129,7 +129,7 @@ __global__ void __launch_bounds__(256) k_plan_tiles_table(const uint32_t* __rest
       tiles[t] = tile;
       atomicAdd(&stats[0], (unsigned long long)tile.rows * __popc(mask));
       atomicAdd(&stats[1], (unsigned long long)s_act);
-      atomicAdd(&hist[s_part + __popc(mask)], 1);       // tiles of this window and part with this many taps (k_plan_perm)
+      if (hist) atomicAdd(&hist[s_part + __popc(mask)], 1);       // tiles of this part with this many taps (k_plan_perm)
     }
   }
   uint32_t big = 0;         // the largest present entry: lets the bounds check skip its scan when every entry is in range
@@ -161,12 +161,11 @@ __global__ void __launch_bounds__(256) k_plan_tiles_table(const uint32_t* __rest
   }
 }
 
-// perm[position] = tile.  Within every window of `win` consecutive tiles of a part ([b0,b1) and [b1,b2)) the tiles come by
-// falling tap count; windows keep the plan's order, because a plan over a large map sorts inside runs of caller rows to
-// keep the gathers of concurrently running tiles L2-local (win = a few rounds of the SMs; for a map sorted as one block
-// the window is the whole part).  hist[(window * 2 + part) * 32 + taps] holds the tile counts (k_plan_tiles_table),
-// cursor[] the next free slot of each bin.  Which of two tiles with the same tap count comes first is left to the order
-// of the atomics: it changes who computes a tile, never a result.
+// perm[position] = tile: the tiles of each part ([b0,b1) and [b1,b2)) by falling tap count, within windows of `win`
+// consecutive tiles (the whole part as it is used: windows of a few rounds were tried for plans over large maps, whose tile
+// order keeps the gathers L2-local, and did not pay).  hist[(window * 2 + part) * 32 + taps] holds the tile counts
+// (k_plan_tiles_table), cursor[] the next free slot of each bin.  Which of two tiles with the same tap count comes first
+// is left to the order of the atomics: it changes who computes a tile, never a result.
 __global__ void k_plan_perm(const PlanTile* __restrict__ tiles, const int* __restrict__ bounds, const int* __restrict__ hist,
                             int* __restrict__ cursor, int win, int* __restrict__ perm) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
@@ -202,7 +201,7 @@ int plan_tiles_table(t2sc_ctx* ctx, t2sc_plan* p, const int32_t* gray, const int
     k_plan_tiles_table<256, HEADER><<<(unsigned)p->max_tiles, 256, 0, ctx->stream>>>(p->nbr, gray, p->src, p->order, gcnt, ngroups, p->split ? 1 : 0, p->n_out,
                                                                                        p->tiles, p->bounds, p->stats, p->tnbr, (uint32_t*)(p->meta + 11), hist, win);
   T2_LAUNCHED(ctx);
-  if (HEADER) {
+  if (HEADER && hist) {
     const i64 bins = (cdiv_i(p->max_tiles, win) + 1) * 64;
     k_plan_perm<<<(unsigned)cdiv_i(p->max_tiles, 256), 256, 0, ctx->stream>>>(p->tiles, p->bounds, hist, hist + bins, win, p->perm);
     T2_LAUNCHED(ctx);
@@ -295,13 +294,16 @@ static int plan_create(t2sc_ctx* ctx, const uint32_t* nbr, const int32_t* gray, 
       PL(scratch.get(&tmp, tb));
       PL(cub::DeviceRadixSort::SortPairs(tmp, tb, keys, keys2, iota, p->order, (int)m, 0, key_bits, ctx->stream));
     }
-    // The order the conv's CTAs take the tiles in (k_plan_perm): by tap count within windows of four rounds of the SMs when
-    // the rows were sorted inside runs (large maps), within the whole part when they were sorted as one block.
-    const int win = block_rows >= m ? (1 << 30) : 4 * ctx->num_sms;
-    const i64 bins = (cdiv_i(p->max_tiles, win) + 1) * 64;
+    // The order the conv's CTAs take the tiles in (k_plan_perm): by tap count when the rows were sorted as one block; plan
+    // order when they were sorted inside runs (large maps: the runs keep concurrently running tiles L2-local).
+    p->balanced = block_rows >= m;
+    const int win = 1 << 30;
+    const i64 bins = 2 * 64;
     int* hist = nullptr;
-    PL(scratch.get(&hist, (size_t)(2 * bins)));
-    PL(cudaMemsetAsync(hist, 0, (size_t)(2 * bins) * sizeof(int), ctx->stream));
+    if (p->balanced) {
+      PL(scratch.get(&hist, (size_t)(2 * bins)));
+      PL(cudaMemsetAsync(hist, 0, (size_t)(2 * bins) * sizeof(int), ctx->stream));
+    }
     if (plan_tiles_table<true>(ctx, p, gray, p->meta, ngroups, hist, win) != T2SC_OK) return fail(cudaGetLastError());
   }
 #undef PL
