@@ -347,9 +347,18 @@ __device__ __forceinline__ void epilogue_row(const ConvArgs& a, uint32_t taddr, 
         hp[i] = pack2<T>(h.x + to_f<T>(sx[(col + 2 * i) / a.ep.skip_rep]), h.y + to_f<T>(sx[(col + 2 * i + 1) / a.ep.skip_rep]));
       }
     }
-    uint4* yp = (uint4*)(y + (i64)orow * a.Co + col);
+    // the block's 64 bytes as two 32-byte stores (whole sectors) when the row allows it, else four 16-byte ones
+    T* const yb = y + (i64)orow * a.Co + col;
+    if (((uintptr_t)yb & 31) == 0) {
 #pragma unroll
-    for (int g = 0; g < 4; g++) yp[g] = make_uint4(hp[g * 4], hp[g * 4 + 1], hp[g * 4 + 2], hp[g * 4 + 3]);
+      for (int g = 0; g < 2; g++)
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(yb + g * 16), "r"(hp[g * 8]), "r"(hp[g * 8 + 1]), "r"(hp[g * 8 + 2]),
+                     "r"(hp[g * 8 + 3]), "r"(hp[g * 8 + 4]), "r"(hp[g * 8 + 5]), "r"(hp[g * 8 + 6]), "r"(hp[g * 8 + 7]) : "memory");
+    } else {
+      uint4* yp = (uint4*)yb;
+#pragma unroll
+      for (int g = 0; g < 4; g++) yp[g] = make_uint4(hp[g * 4], hp[g * 4 + 1], hp[g * 4 + 2], hp[g * 4 + 3]);
+    }
   }
 }
 
