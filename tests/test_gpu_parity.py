@@ -386,6 +386,30 @@ def test_map_entries_past_the_feature_array_are_reported(sp):
     check_feats(host(good), oracle.conv_block(x, w, b, oracle.build_neighbors(c)[0], "bf16"), "context still usable")
 
 
+def test_output_that_is_only_16_byte_aligned(sp):
+    """The epilogue stores a 32-column block as two 32-byte stores when the output row allows it and as four 16-byte ones
+    otherwise: an output array that starts 16 bytes into a 32-byte line must give the same bits."""
+    rng = np.random.default_rng(16)
+    n, C = 3000, 128
+    c = random_coords(rng, n, 24)
+    cache = sp.build_neighbors(dev(c))
+    x = dev(rounded(rng.standard_normal((n, C)), "bf16"), torch.bfloat16)
+    w = dev(rounded(scenes.kaiming_uniform_weight(C, C, 16), "bf16"), torch.bfloat16)
+    b = dev(rounded(0.1 * rng.standard_normal(C), "bf16"), torch.bfloat16)
+    y_ref = sp.subm_conv(x, w, b, cache, act="silu")
+    assert y_ref.data_ptr() % 32 == 0
+    buf = torch.zeros(n * C + 8, dtype=torch.bfloat16, device="cuda")
+    y_odd = buf[8:].view(n, C)
+    assert y_odd.data_ptr() % 32 == 16
+    sp.subm_conv(x, w, b, cache, act="silu", out=y_odd)
+    assert torch.equal(y_odd, y_ref)
+    assert float(buf[:8].abs().sum()) == 0.0
+    lin_ref = sp.linear(x, w[:, 13, :].contiguous(), b)
+    sp.linear(x, w[:, 13, :].contiguous(), b, out=y_odd)
+    assert torch.equal(y_odd, lin_ref)
+    cache.ctx.device_status()
+
+
 def test_add_skip_and_gather_rows_standalone(sp):
     """k_add_skip / k_gather_rows of the reference (src/sdec.cu:34-43) as stand-alone operators, 8 channels per thread
     and the scalar form (Co % 8 != 0), against the oracle; fp32 add, one rounding."""
