@@ -423,8 +423,7 @@ def run_single_conv(args, rank, world, local_rank, dev):
             "roofline": roof, "clocks": clocks, "gpu_launches": launches,
             "e2e": None}
     # Both ways of driving the host-buffer entry point are measured; the line's headline is the faster one on this host
-    # (with eight ranks on one host the copies of all ranks share its memory and PCIe roots, and more calls in flight
-    # per rank can lose).
+    # (in multi-rank runs several calls in flight per rank have been the slower way).
     piped = e2e_pipe_ms == e2e_pipe_ms and e2e_pipe_ms <= e2e_total
     e2e_best = e2e_pipe_ms if piped else e2e_total
     line["e2e"] = {"value": flops_all / (e2e_best * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_best,
