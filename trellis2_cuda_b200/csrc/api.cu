@@ -1,5 +1,6 @@
 // C-ABI entry points that are not kernels themselves: context, errors, conv dispatch, host-buffer call.
 #include "common.cuh"
+#include <sched.h>
 
 static char g_create_err[512] = {0};
 
@@ -50,6 +51,18 @@ extern "C" int t2sc_ctx_create(int device, void* stream, t2sc_ctx** out) {
   return T2SC_OK;
 }
 
+// Waits for the context's stream by polling an event and yielding the core between polls.  cudaStreamSynchronize was
+// seen to keep other host threads of the process, each driving its own context, from issuing their calls while it waited
+// (three complete host-buffer calls in flight then took as long as three calls one after the other); a blocking-sync
+// event cured that but added ~0.4 ms to a single call.  A poll returns at once, so nothing is held between polls.
+static cudaError_t ctx_wait(t2sc_ctx* ctx) {
+  cudaError_t e;
+  if (!ctx->done && (e = cudaEventCreateWithFlags(&ctx->done, cudaEventDisableTiming)) != cudaSuccess) return e;
+  if ((e = cudaEventRecord(ctx->done, ctx->stream)) != cudaSuccess) return e;
+  while ((e = cudaEventQuery(ctx->done)) == cudaErrorNotReady) sched_yield();
+  return e;
+}
+
 extern "C" int t2sc_ctx_destroy(t2sc_ctx* ctx) {
   if (!ctx) return T2SC_OK;
   cudaSetDevice(ctx->device);
@@ -57,6 +70,7 @@ extern "C" int t2sc_ctx_destroy(t2sc_ctx* ctx) {
   if (ctx->arena) cudaFreeAsync(ctx->arena, ctx->stream);
   cudaStreamSynchronize(ctx->stream);
   cudaFree(ctx->status);
+  if (ctx->done) cudaEventDestroy(ctx->done);
   if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
   delete ctx;
   return T2SC_OK;
@@ -64,7 +78,7 @@ extern "C" int t2sc_ctx_destroy(t2sc_ctx* ctx) {
 
 extern "C" int t2sc_ctx_sync(t2sc_ctx* ctx) {
   T2_REQ(ctx, ctx != nullptr, "null context");
-  T2_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  T2_CUDA(ctx, ctx_wait(ctx));
   return T2SC_OK;
 }
 
@@ -260,7 +274,7 @@ extern "C" int t2sc_subm_conv_host(t2sc_ctx* ctx, const int32_t* coords_host, in
   t2sc_epilogue ep; memset(&ep, 0, sizeof(ep)); ep.bias = b;
   if ((rc = t2sc_subm_conv(ctx, plan, x, w, &ep, y, dtype, n, Ci, Co, T2SC_VARIANT_AUTO)) != T2SC_OK) { cleanup(); return rc; }
   HOST_TRY(cudaMemcpyAsync(y_host, y, (size_t)n * Co * es, cudaMemcpyDeviceToHost, ctx->stream));
-  HOST_TRY(cudaStreamSynchronize(ctx->stream));
+  HOST_TRY(ctx_wait(ctx));
 #undef HOST_TRY
   cleanup();
   int st = 0;

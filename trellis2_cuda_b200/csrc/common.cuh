@@ -22,6 +22,7 @@ struct t2sc_ctx {
   char* arena = nullptr;        // scratch arena of the entry points (see Scratch), arena_bytes long; grown to arena_want
   size_t arena_bytes = 0, arena_want = 0;
   int* status = nullptr;        // device word; kernels OR an error code into it when a bounded wait gives up
+  cudaEvent_t done = nullptr;   // event the host polls when it waits for the stream (see ctx_wait in api.cu)
   char err[1024] = {0};
 };
 
